@@ -26,15 +26,22 @@ from typing import Dict, Hashable, List, Optional
 
 import torch
 
-from ..parts.base import FixedStateNeed, PagedKVNeed, PagedKVView, StateView
+from ..parts.base import FixedStateNeed, PagedKVNeed, PagedKVView, PagedRowsNeed, StateView
 from .pages import PageError, PagePool, SlotPool
 
 RELEASED = -1      # block-table entry of a block that was given back (or never existed)
 GUARD_VALUE = -24576.0     # exact in bf16 and fp32; what a guard page holds
 
 
-def group_key(need: PagedKVNeed) -> str:
+def group_key(need) -> str:
     return "full" if need.window is None else f"window{int(need.window)}"
+
+
+def page_shape(need, page_size: int):
+    """What one page of a paged entry holds: keys and values of every kv head, or one row per token."""
+    if isinstance(need, PagedRowsNeed):
+        return (page_size, need.width)
+    return (2, need.num_kv_heads, page_size, need.head_dim)
 
 
 @dataclass
@@ -74,14 +81,14 @@ class CacheManager:
         self.guarded: Dict[str, torch.Tensor] = {}       # entry -> the whole allocation, guards included
         for name, need in entries.items():
             need = getattr(need, "need", need)
-            if isinstance(need, PagedKVNeed):
+            if isinstance(need, (PagedKVNeed, PagedRowsNeed)):
                 key = group_key(need)
                 if key not in self.groups:
                     self.groups[key] = CacheGroup(key, need.window, self.pages_for_group(need.window, max_step_tokens))
                 self.entry_group[name] = key
                 if device is not None:
                     pages = self.groups[key].pool.num_pages + 1        # the pool's pages, then the spare page (see pad_page)
-                    whole = torch.zeros((pages + (2 if guard_pages else 0), 2, need.num_kv_heads, page_size, need.head_dim),
+                    whole = torch.zeros((pages + (2 if guard_pages else 0), *page_shape(need, page_size)),
                                         dtype=need.dtype or kv_dtype, device=device)
                     if guard_pages:
                         whole[0].fill_(GUARD_VALUE)

@@ -1,8 +1,9 @@
 from .spec import PartSpec, LayerSpec, RunSpec, ModelSpec
 from .qwen2 import Qwen2Config, ConfigError, preset, PRESETS
+from .gedalix import GedalixConfig, gedalix_preset
 from .registry import (Architecture, register_architecture, get_architecture, architectures,
                        architecture_of, architecture_for, find_preset, parameter_count, load_config)
 
-__all__ = ["PartSpec", "LayerSpec", "RunSpec", "ModelSpec", "Qwen2Config", "ConfigError", "preset",
+__all__ = ["PartSpec", "LayerSpec", "RunSpec", "ModelSpec", "Qwen2Config", "GedalixConfig", "gedalix_preset", "ConfigError", "preset",
            "PRESETS", "Architecture", "register_architecture", "get_architecture", "architectures",
            "architecture_of", "architecture_for", "find_preset", "parameter_count", "load_config"]

@@ -50,7 +50,9 @@ def architectures() -> Dict[str, Architecture]:
 def architecture_of(raw_config: Dict[str, Any]) -> Architecture:
     """Choose the architecture from a parsed config.json."""
     _ensure_builtin()
-    names = raw_config.get("architectures") or []
+    names = list(raw_config.get("architectures") or [])
+    if isinstance(raw_config.get("architecture"), str):          # some families name theirs in the singular
+        names.append(raw_config["architecture"])
     for n in names:
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]
@@ -121,4 +123,4 @@ def _ensure_builtin() -> None:
     global _loaded
     if not _loaded:
         _loaded = True
-        from ..models import qwen2  # noqa: F401  (registers itself)
+        from ..models import gedalix, qwen2  # noqa: F401  (they register themselves)

@@ -56,10 +56,13 @@ class RunSpec:
                    place in the list, so a layer that runs twice gets two caches)
     read_cache_of  index into `ModelSpec.order` of an EARLIER run whose cache this
                    run reads instead of writing one of its own
+    entry          a part (registry of run entries) that changes the residual stream right
+                   before this run's layer: what a pass of looped layers adds first
     """
     layer: int
     cache: Optional[str] = None
     read_cache_of: Optional[int] = None
+    entry: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -74,6 +77,8 @@ class ModelSpec:
     order: List[RunSpec]
     final_norm: PartSpec
     head: PartSpec
+    # names a checkpoint may carry although no part asks for them (tensors of a sub-layer that a layer leaves out)
+    tolerated_tensors: tuple = ()
 
     def validate(self) -> None:
         if self.hidden_size <= 0 or self.vocab_size <= 0 or self.max_position <= 0:

@@ -83,6 +83,14 @@ _SIGNATURES = {
                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                       c_float, c_void_p, c_void_p],
     },
+    "residual.cu": {
+        "mlb_embed_gather_scaled": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+        "mlb_add_table_rows": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mlb_add_scaled_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                   c_float, c_void_p],
+        "mlb_add_scaled_inplace": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p],
+        "mlb_stream_entry": [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p],
+    },
     "sampling.cu": {
         "mlb_argmax_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
         "mlb_sample_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -140,6 +148,12 @@ def base_sources():
             ("sampling.cu", {}), ("replay.cu", {})]
 
 
+def part_sources():
+    """(source, defines) of the kernels that only some kinds of parts ask for (each part names its own in
+    `kernel_sources`)."""
+    return [("residual.cu", {}), ("grouped_gemm.cu", {}), ("latent.cu", {}), ("moe.cu", {})]
+
+
 def all_sources():
     """Every object the package can ask for with its default head sizes: what the build
     check compiles."""
@@ -148,7 +162,7 @@ def all_sources():
     for d in (32, 64, 128):
         out += attention.mma_sources(d) + attention.tc_sources(d)
     from . import gemm_bf16
-    return out + gemm_bf16.sources() + [("gemv_noalloc.cu", {})]
+    return out + gemm_bf16.sources() + [("gemv_noalloc.cu", {})] + part_sources()
 
 
 # ------------------------------------------------------------------------------ basic
@@ -288,6 +302,67 @@ def copy_raw(dst: int, src: int, nbytes: int, to_device: bool) -> None:
     status = L.mlb_copy_async(dst, src, nbytes, 1 if to_device else 0, _stream())
     if status != 0:
         build.check(L, status)
+
+
+# ------------------------------------------------------------------------------ scaled residual stream
+def embed_gather_scaled(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float) -> None:
+    """out[t] = table[ids[t]] * scale (fp32)."""
+    _need(table, "table", dims=2); _need(ids, "ids", torch.int32, 1); _need(out, "out", torch.float32, 2)
+    vocab, width = table.shape
+    if out.shape != (ids.shape[0], width):
+        raise KernelError(f"embed_gather_scaled: out {tuple(out.shape)} does not match ({ids.shape[0]}, {width})")
+    L = lib("residual.cu")
+    build.check(L, L.mlb_embed_gather_scaled(table.data_ptr(), dtype_tag(table), ids.data_ptr(), out.data_ptr(),
+                                             ids.shape[0], width, vocab, float(scale), _stream()))
+
+
+def add_table_rows(x: torch.Tensor, table: torch.Tensor, index: torch.Tensor) -> None:
+    """x[t] += table[index[t]] (fp32 sum; an index outside the table leaves NaN)."""
+    _need(x, "x", torch.float32, 2); _need(table, "table", dims=2); _need(index, "index", torch.int32, 1)
+    if table.shape[1] != x.shape[1] or index.shape[0] != x.shape[0]:
+        raise KernelError("add_table_rows: shapes do not agree")
+    L = lib("residual.cu")
+    build.check(L, L.mlb_add_table_rows(x.data_ptr(), table.data_ptr(), dtype_tag(table), index.data_ptr(), x.shape[0],
+                                        x.shape[1], table.shape[0], _stream()))
+
+
+def add_scaled_rmsnorm(residual: torch.Tensor, delta: torch.Tensor, col_scale: Optional[torch.Tensor], weight: torch.Tensor,
+                       eps: float, out: torch.Tensor) -> None:
+    """residual += col_scale * delta (per column; a [S, M, N] delta is summed over S first), then out = rmsnorm(residual)."""
+    _need(residual, "residual", torch.float32, 2); _need(weight, "weight", torch.float32, 1); _need(out, "out", dims=2)
+    n_delta, stride = _partials(delta, residual.shape, "add_scaled_rmsnorm delta")
+    if out.shape != residual.shape or weight.shape[0] != residual.shape[1]:
+        raise KernelError("add_scaled_rmsnorm: shapes do not agree")
+    if col_scale is not None:
+        _need(col_scale, "col_scale", torch.float32, 1)
+        if col_scale.shape[0] != residual.shape[1]:
+            raise KernelError("add_scaled_rmsnorm: one factor per column")
+    L = lib("residual.cu")
+    build.check(L, L.mlb_add_scaled_rmsnorm(residual.data_ptr(), delta.data_ptr(), n_delta, stride, _ptr(col_scale),
+                                            weight.data_ptr(), out.data_ptr(), dtype_tag(out), residual.shape[0],
+                                            residual.shape[1], float(eps), _stream()))
+
+
+def add_scaled_inplace(x: torch.Tensor, delta: torch.Tensor, col_scale: Optional[torch.Tensor]) -> None:
+    """x += col_scale * delta (per column of a 2-D x; partial sums as in add_inplace)."""
+    _need(x, "x", torch.float32, 2)
+    n_delta, stride = _partials(delta, x.shape, "add_scaled_inplace delta")
+    if col_scale is not None:
+        _need(col_scale, "col_scale", torch.float32, 1)
+        if col_scale.shape[0] != x.shape[1]:
+            raise KernelError("add_scaled_inplace: one factor per column")
+    L = lib("residual.cu")
+    build.check(L, L.mlb_add_scaled_inplace(x.data_ptr(), delta.data_ptr(), n_delta, stride, _ptr(col_scale), x.shape[1],
+                                            x.numel(), _stream()))
+
+
+def stream_entry(x: torch.Tensor, x0: Optional[torch.Tensor], vector: torch.Tensor) -> None:
+    """x[t] += x0[t] (when given) + vector."""
+    _need(x, "x", torch.float32, 2); _need(vector, "vector", torch.float32, 1)
+    if vector.shape[0] != x.shape[1] or (x0 is not None and (x0.shape != x.shape or x0.dtype != torch.float32 or not x0.is_contiguous())):
+        raise KernelError("stream_entry: shapes do not agree")
+    L = lib("residual.cu")
+    build.check(L, L.mlb_stream_entry(x.data_ptr(), _ptr(x0), vector.data_ptr(), x.shape[1], x.numel(), _stream()))
 
 
 # ------------------------------------------------------------------------------ small host -> device uploads

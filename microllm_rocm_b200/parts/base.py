@@ -68,6 +68,15 @@ class PagedKVNeed:
 
 
 @dataclass(frozen=True)
+class PagedRowsNeed:
+    """One row of `width` elements per token, shared by all heads, that grows with the tokens (a compressed
+    key/value cache).  Pages, block tables and windows as for PagedKVNeed; a page is [page_size, width]."""
+    width: int
+    window: Optional[int] = None
+    dtype: Optional[torch.dtype] = None
+
+
+@dataclass(frozen=True)
 class FixedStateNeed:
     """Per-request state of a fixed size, whatever the number of tokens."""
     shape: Tuple[int, ...]
@@ -76,7 +85,7 @@ class FixedStateNeed:
 
 @dataclass
 class PagedKVView:
-    pages: torch.Tensor            # [num_pages, 2, NKV, page_size, D]
+    pages: torch.Tensor            # [num_pages, 2, NKV, page_size, D]; for a PagedRowsNeed [num_pages, page_size, width]
     block_table: torch.Tensor      # [A, max_blocks] int32, this step's sequences, this group
     page_size: int
     writable: bool                 # False: the run reads a cache another run wrote
@@ -247,10 +256,21 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
-class Block:
+class RunEntry(Part):
+    """Something a run of the execution list does to the residual stream before its layer (what a pass of looped
+    layers adds first, say).  `needs_embedding`: forward wants the embedding output of this step as well."""
+    needs_embedding = False
+
+    def forward(self, residual: torch.Tensor, ctx: StepContext, embedding_output: Optional[torch.Tensor]) -> None:
+        """Changes `residual` in place; a delta that is still pending is added later, which commutes."""
+        raise NotImplementedError
+
+
+class Block(Part):
     """Arrangement of two norms, a mixer and a feed-forward around the residual stream.
     `forward` gets the residual and a delta not yet added to it (or None) and returns the
-    same pair, so the add can be fused into whichever norm comes next."""
+    same pair, so the add can be fused into whichever norm comes next.  A block may own tensors
+    (per-column scales of what it adds): it declares and receives them like any part, under the layer's prefix."""
 
     def __init__(self, params, rt, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, feed_forward: FeedForward):
         raise NotImplementedError
@@ -276,6 +296,7 @@ FEED_FORWARDS: Dict[str, Callable] = {}
 BLOCKS: Dict[str, Callable] = {}
 EMBEDDINGS: Dict[str, Callable] = {}
 HEADS: Dict[str, Callable] = {}
+RUN_ENTRIES: Dict[str, Callable] = {}
 
 
 def _register(table: Dict[str, Callable], what: str):
@@ -296,6 +317,7 @@ register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_block = _register(BLOCKS, "block")
 register_embedding = _register(EMBEDDINGS, "embedding")
 register_head = _register(HEADS, "head")
+register_run_entry = _register(RUN_ENTRIES, "run entry")
 
 
 def make(table: Dict[str, Callable], what: str, spec, *args, **kwargs):

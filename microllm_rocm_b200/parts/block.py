@@ -1,14 +1,34 @@
-"""Pre-norm residual block:  x += mixer(norm1(x));  x += feed_forward(norm2(x)).
+"""Pre-norm residual block:  x += a1 * mixer(norm1(x));  x += a2 * feed_forward(norm2(x)).
 Each residual add is fused into the norm that follows it (the reference does so on its
 decode path only: src/model/model.cpp:862-870 `add_rms_norm`), so the block passes the
-residual stream on together with a delta that has not been added yet."""
+residual stream on together with a delta that has not been added yet.
+
+a1 and a2 are 1 unless the block is given `residual_scale` (a number m) and/or `layer_scale` (the local names of
+two learned per-column vectors s1, s2): then a1 = m * s1 and a2 = m * s2, element by element, in fp32.  a1 is
+applied where the mixer's result is added; a2 is handed to a feed-forward that can multiply its own result
+(`FeedForward.scales_output`), else applied by one more pass over the result.  The delta a block returns is always
+ready to be added as it is.  A layer may have no feed-forward (kind "none"): the block then ends after the mixer."""
 from __future__ import annotations
 
-from typing import Optional
+from typing import Dict, Optional
 
 import torch
 
-from .base import Block, FeedForward, Mixer, Norm, Runtime, StepContext, register_block
+from ..kernels import ops
+from .base import (Block, FeedForward, Mixer, Norm, Runtime, StepContext, WeightSpec, register_block,
+                   register_feed_forward)
+
+
+@register_feed_forward("none")
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward."""
+    absent = True
+
+    def __init__(self, params: dict, rt: Runtime):
+        pass
+
+    def replay_key(self):
+        return ("none",)
 
 
 @register_block("pre_norm_residual")
@@ -16,14 +36,43 @@ class PreNormResidualBlock(Block):
     def __init__(self, params: dict, rt: Runtime, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm,
                  feed_forward: FeedForward):
         self.rt = rt
+        self.prefix = params.get("prefix", "")
         self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward = mixer_norm, mixer, ffn_norm, feed_forward
+        self.has_ff = not getattr(feed_forward, "absent", False)
+        self.residual_scale = float(params.get("residual_scale", 1.0))
+        self.layer_scale = tuple(params["layer_scale"]) if params.get("layer_scale") else None   # (name of s1, name of s2)
+        self.size = int(params["size"]) if self.layer_scale or self.residual_scale != 1.0 else 0
+        self.scaled = bool(self.layer_scale) or self.residual_scale != 1.0
+        self.a1: Optional[torch.Tensor] = None
+        self.a2: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        if not self.layer_scale:
+            return {}
+        names = self.layer_scale if self.has_ff else self.layer_scale[:1]
+        return {n: WeightSpec((self.size,), role="vector", init=("one_plus_normal", 0.1)) for n in names}
+
+    def kernel_sources(self):
+        return [("residual.cu", {})] if self.scaled else []
+
+    def bind(self, tensors):
+        if not self.scaled:
+            return
+        m = self.residual_scale
+        device = self.rt.device
+        one = lambda name: (tensors[name] * m).contiguous() if self.layer_scale else torch.full((self.size,), m, dtype=torch.float32, device=device)
+        self.a1 = one(self.layer_scale[0] if self.layer_scale else None)
+        self.a2 = one(self.layer_scale[1] if self.layer_scale else None) if self.has_ff else None
 
     def replay_key(self):
         keys = [p.replay_key() for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)]
-        return None if any(k is None for k in keys) else ("pre_norm_residual", self.rt.dtype, *keys)
+        if not self.has_ff:
+            return None                  # the block returns no pending delta: its runs are issued call by call
+        return None if any(k is None for k in keys) else ("pre_norm_residual", self.rt.dtype, self.scaled, *keys)
 
     def own_tensors(self):
-        return [t for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) for t in p.own_tensors()]
+        own = [t for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) for t in p.own_tensors()]
+        return own + [self.a1, self.a2]
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext, cache):
         normed = ctx.buffer("block.normed", tuple(residual.shape), self.rt.dtype)
@@ -32,6 +81,24 @@ class PreNormResidualBlock(Block):
         else:
             self.mixer_norm.add_forward(residual, delta, normed)
         mixed = self.mixer.forward(normed, ctx, cache)
+        if not self.has_ff:
+            if self.scaled:
+                ops.add_scaled_inplace(residual, mixed, self.a1)
+            else:
+                ops.add_inplace(residual, mixed)
+            return residual, None
         normed2 = ctx.buffer("block.normed2", tuple(residual.shape), self.rt.dtype)
-        self.ffn_norm.add_forward(residual, mixed, normed2)
-        return residual, self.feed_forward.forward(normed2, ctx)
+        if self.scaled:
+            self.ffn_norm.add_forward(residual, mixed, normed2, scale=self.a1)
+        else:
+            self.ffn_norm.add_forward(residual, mixed, normed2)
+        if not self.scaled:
+            return residual, self.feed_forward.forward(normed2, ctx)
+        if getattr(self.feed_forward, "scales_output", False):
+            return residual, self.feed_forward.forward(normed2, ctx, out_scale=self.a2)
+        # a feed-forward that cannot scale its own result: one pass over it (split partial sums are added up on the way)
+        out = self.feed_forward.forward(normed2, ctx)
+        scaled = ctx.buffer("block.scaled_delta", tuple(residual.shape), torch.float32)
+        scaled.zero_()
+        ops.add_scaled_inplace(scaled, out, self.a2)
+        return residual, scaled

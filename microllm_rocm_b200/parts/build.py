@@ -14,7 +14,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..config.spec import ModelSpec
-from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Part, Runtime,
+from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, RUN_ENTRIES, Part, Runtime,
                    StepContext, WeightSpec, make)
 
 
@@ -54,6 +54,15 @@ class Model:
             for part, ps in ((mixer_norm, layer.mixer_norm), (mixer, layer.mixer), (ffn_norm, layer.ffn_norm),
                              (feed_forward, layer.feed_forward)):
                 self._parts.append((layer.prefix + ps.params.get("prefix", ""), part))
+            self._parts.append((layer.prefix + layer.block.params.get("prefix", ""), block))
+        # what a run does to the residual stream before its layer
+        self.run_entries = []
+        for run in spec.order:
+            entry = make(RUN_ENTRIES, "run entry", run.entry, rt) if run.entry is not None else None
+            self.run_entries.append(entry)
+            if entry is not None:
+                self._parts.append((run.entry.params.get("prefix", ""), entry))
+        self._keep_embedding = any(e is not None and e.needs_embedding for e in self.run_entries)
         # caches: one entry per owning run
         self.cache_entries: Dict[str, CacheEntry] = {}
         self.run_cache: List[Tuple[Optional[str], bool]] = []    # per run: (cache name, owns it)
@@ -125,7 +134,8 @@ class Model:
         """Names a checkpoint may carry although no part wants them: a redundant head matrix
         when the head is tied to the embedding table."""
         params = self.spec.head.params
-        return [params["name"]] if params.get("tied_to") is not None and "name" in params else []
+        tied = [params["name"]] if params.get("tied_to") is not None and "name" in params else []
+        return tied + list(self.spec.tolerated_tensors)
 
     def placements(self):
         """Where each checkpoint tensor goes on the device.  Returns (destinations, pieces):
@@ -182,6 +192,10 @@ class Model:
         sink = ctx.tensor_sink
         if sink is not None:
             sink("embedding", residual)
+        embedding_output = None
+        if self._keep_embedding:                 # a later run adds the embedding output again: the residual is changed in place
+            embedding_output = ctx.buffer("model.embedding_output", tuple(residual.shape), torch.float32)
+            embedding_output.copy_(residual)
         keys = self._layer_replay_keys() if self.replay_layers and sink is None else None
         recordings = {}                      # structure of a run -> (recording, the recorded run's own pointers) | None
         for i, run in enumerate(self.spec.order):
@@ -192,6 +206,8 @@ class Model:
                 if not owns:
                     view = _read_only(view)
             block = self.blocks[run.layer]
+            if self.run_entries[i] is not None:
+                self.run_entries[i].forward(residual, ctx, embedding_output)
             key = keys[i] if keys is not None and i > 0 and delta is not None else None
             if key is None:
                 # the first run of a step plans launches and makes the step's tables: it always runs call by call

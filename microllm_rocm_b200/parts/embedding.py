@@ -19,18 +19,25 @@ class TokenEmbedding(Part):
         self.name = params["name"]
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
+        self.scale = float(params.get("scale", 1.0))       # the gathered rows are multiplied by it (fp32)
         self.rt = rt
         self.table: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {self.name: WeightSpec((self.vocab, self.hidden), role="table")}
 
+    def kernel_sources(self):
+        return [("residual.cu", {})] if self.scale != 1.0 else []
+
     def bind(self, tensors):
         self.table = tensors[self.name]
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = torch.empty((token_ids.shape[0], self.hidden), dtype=torch.float32, device=token_ids.device)
-        ops.embed_gather(self.table, token_ids, out)
+        if self.scale != 1.0:
+            ops.embed_gather_scaled(self.table, token_ids, out, self.scale)
+        else:
+            ops.embed_gather(self.table, token_ids, out)
         return out
 
 

@@ -18,27 +18,29 @@ class SwiGLU(FeedForward):
         self.prefix = params.get("prefix", "")
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
+        # local names of the three matrices in the checkpoint (gate, up, down)
+        self.n_gate, self.n_up, self.n_down = params.get("names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
         self.rt = rt
         self.w_gate_up = self.w_down = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {"gate_proj.weight": WeightSpec((self.inter, self.hidden)),
-                "up_proj.weight": WeightSpec((self.inter, self.hidden)),
-                "down_proj.weight": WeightSpec((self.hidden, self.inter))}
+        return {self.n_gate: WeightSpec((self.inter, self.hidden)),
+                self.n_up: WeightSpec((self.inter, self.hidden)),
+                self.n_down: WeightSpec((self.hidden, self.inter))}
 
     def kernel_sources(self):
         return [] if self.rt.is_fp32 else gemm_bf16.sources(engine_only=True)
 
     def fused_tensors(self):
         return {"gate_up_proj.weight": (WeightSpec((2 * self.inter, self.hidden)),
-                                        [("gate_proj.weight", 0), ("up_proj.weight", self.inter)])}
+                                        [(self.n_gate, 0), (self.n_up, self.inter)])}
 
     def bind(self, tensors):
         if "gate_up_proj.weight" in tensors:             # from the loader: already fused, gate rows then up rows
             self.w_gate_up = tensors["gate_up_proj.weight"]
         else:
-            self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], 0).contiguous()
-        self.w_down = tensors["down_proj.weight"]
+            self.w_gate_up = torch.cat([tensors[self.n_gate], tensors[self.n_up]], 0).contiguous()
+        self.w_down = tensors[self.n_down]
 
     def replay_key(self):
         if not self.rt.is_fp32 and not gemm_bf16._direct_library(self.rt.device):

@@ -16,14 +16,18 @@ class RMSNorm(Norm):
         self.prefix = params.get("prefix", "")
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.name = params.get("name", "weight")         # the weight's local name in the checkpoint
+        self.absent = bool(params.get("absent", False))  # a norm in front of a sub-layer that the layer leaves out: no weight, never run
         self.rt = rt
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {"weight": WeightSpec((self.size,), role="vector", init=("one_plus_normal", 0.1))}
+        if self.absent:
+            return {}
+        return {self.name: WeightSpec((self.size,), role="vector", init=("one_plus_normal", 0.1))}
 
     def bind(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors.get(self.name) if self.absent else tensors[self.name]
 
     def replay_key(self):
         return ("rmsnorm", self.size, self.eps)
@@ -34,5 +38,9 @@ class RMSNorm(Norm):
     def forward(self, x, out, rows=None):
         ops.rmsnorm(x, self.weight, self.eps, out, rows=rows)
 
-    def add_forward(self, residual, delta, out):
-        ops.add_rmsnorm(residual, delta, self.weight, self.eps, out)
+    def add_forward(self, residual, delta, out, scale=None):
+        """`scale` [width] fp32: the delta is multiplied by it, column by column, before it is added."""
+        if scale is not None:
+            ops.add_scaled_rmsnorm(residual, delta, scale, self.weight, self.eps, out)
+        else:
+            ops.add_rmsnorm(residual, delta, self.weight, self.eps, out)

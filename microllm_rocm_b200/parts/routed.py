@@ -1,0 +1,142 @@
+"""Routed experts: every token runs `top` of `experts` small gated feed-forwards and adds their results up.
+
+  z = Wr x + b                       fp32
+  chosen = the `top` largest z;  w = softmax over the chosen z only
+  y = sum_j w_j * down_e(silu(gate_e x) * up_e x)          e = chosen_j
+  y += sigmoid(Wsg x) * shared(x)    a shared expert of the same form that every token runs (optional, its gate too)
+
+Nothing is counted on the host: the router writes the choices, a kernel sorts the (token, choice) pairs by expert,
+and two grouped products (`kernels/grouped.py`) walk the sorted list, so the part is safe to capture.  The experts'
+matrices live stacked on the device ([E, 2 ff, W] gate over up, and [E, W, ff]); the loader streams every expert's
+pieces straight into their rows.  The shared expert is the ordinary gated feed-forward part under its own prefix.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..kernels import grouped, moe, ops
+from .base import FEED_FORWARDS, FeedForward, Runtime, StepContext, WeightSpec, make, register_feed_forward, scratch
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    scales_output = True          # forward(..., out_scale=) multiplies the result per column
+
+    def __init__(self, params: dict, rt: Runtime):
+        self.prefix = params.get("prefix", "")
+        self.hidden = int(params["hidden_size"])
+        self.experts = int(params["experts"])
+        self.top = int(params["top"])
+        self.inter = int(params["expert_size"])
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"routed experts: top {self.top} of {self.experts}")
+        # local names: expert e's matrices are expert_names[i].format(e); router, its bias, the shared expert's gate row
+        self.expert_names = tuple(params.get("expert_names", ("experts.{}.gate_proj.weight", "experts.{}.up_proj.weight",
+                                                              "experts.{}.down_proj.weight")))
+        self.n_router = params.get("router_name", "router.weight")
+        self.n_router_bias = params.get("router_bias_name")            # None: no bias
+        self.shared = None
+        self.shared_prefix = ""
+        self.n_shared_gate = None
+        shared = params.get("shared")
+        if shared is not None:                                         # a PartSpec of a feed-forward
+            self.shared = make(FEED_FORWARDS, "feed-forward", shared, rt)
+            self.shared_prefix = shared.params.get("prefix", "")
+            self.n_shared_gate = params.get("shared_gate_name")        # None: the shared expert is added ungated
+        self.rt = rt
+        self.w_gate_up = self.w_down = self.w_router = self.b_router = self.w_shared_gate = None
+
+    # --- declarations -----------------------------------------------------------------
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs = {}
+        for e in range(self.experts):
+            g, u, d = (n.format(e) for n in self.expert_names)
+            specs[g] = WeightSpec((self.inter, self.hidden))
+            specs[u] = WeightSpec((self.inter, self.hidden))
+            specs[d] = WeightSpec((self.hidden, self.inter))
+        specs[self.n_router] = WeightSpec((self.experts, self.hidden))
+        if self.n_router_bias:
+            specs[self.n_router_bias] = WeightSpec((self.experts,), role="vector")
+        if self.shared is not None:
+            for name, ws in self.shared.weight_specs().items():
+                specs[self.shared_prefix + name] = ws
+            if self.n_shared_gate:
+                specs[self.n_shared_gate] = WeightSpec((1, self.hidden))
+        return specs
+
+    def fused_tensors(self):
+        ff, E = self.inter, self.experts
+        gate_up, down = [], []
+        for e in range(E):
+            g, u, d = (n.format(e) for n in self.expert_names)
+            gate_up += [(g, e * 2 * ff), (u, e * 2 * ff + ff)]
+            down.append((d, e * self.hidden))
+        fused = {"experts.gate_up": (WeightSpec((E * 2 * ff, self.hidden)), gate_up),
+                 "experts.down": (WeightSpec((E * self.hidden, ff)), down)}
+        if self.shared is not None:
+            for dest, (spec, pieces) in self.shared.fused_tensors().items():
+                fused[self.shared_prefix + dest] = (spec, [(self.shared_prefix + n, row) for n, row in pieces])
+        return fused
+
+    def kernel_sources(self):
+        own = grouped.sources() + moe.sources()
+        return own + (self.shared.kernel_sources() if self.shared is not None else [])
+
+    def bind(self, tensors):
+        ff, E = self.inter, self.experts
+        if "experts.gate_up" in tensors:
+            gate_up, down = tensors["experts.gate_up"], tensors["experts.down"]
+        else:                                  # the checkpoint's pieces: stack them
+            names = [[n.format(e) for n in self.expert_names] for e in range(E)]
+            gate_up = torch.cat([tensors[n] for g, u, _ in names for n in (g, u)], 0).contiguous()
+            down = torch.cat([tensors[d] for _, _, d in names], 0).contiguous()
+        self.w_gate_up = gate_up.view(E, 2 * ff, self.hidden)
+        self.w_down = down.view(E, self.hidden, ff)
+        self.w_router = tensors[self.n_router]
+        self.b_router = tensors[self.n_router_bias] if self.n_router_bias else None
+        if self.shared is not None:
+            n = len(self.shared_prefix)
+            self.shared.bind({k[n:]: v for k, v in tensors.items() if k.startswith(self.shared_prefix)})
+            self.w_shared_gate = tensors[self.n_shared_gate] if self.n_shared_gate else None
+
+    def replay_key(self):
+        shared = None
+        if self.shared is not None:
+            shared = self.shared.replay_key()
+            if shared is None:
+                return None
+        return ("routed_experts", self.hidden, self.experts, self.top, self.inter, shared, self.n_shared_gate is not None,
+                self.b_router is not None)
+
+    def own_tensors(self):
+        own = [self.w_gate_up, self.w_down, self.w_router, self.b_router, self.w_shared_gate]
+        return own + (self.shared.own_tensors() if self.shared is not None else [])
+
+    # --- compute ------------------------------------------------------------------------
+    def forward(self, x: torch.Tensor, ctx: StepContext, out_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T, W, E, top, ff = x.shape[0], self.hidden, self.experts, self.top, self.inter
+        dev, P = x.device, x.shape[0] * self.top
+        flag = ctx.error_flag if ctx is not None else None
+        buf = lambda role, shape, dtype: scratch(ctx, "routed." + role, shape, dtype, dev)
+        ids = buf("ids", (T, top), torch.int32)
+        weights = buf("weights", (T, top), torch.float32)
+        gate = buf("shared_gate", (T,), torch.float32) if self.w_shared_gate is not None else None
+        moe.route(x, self.w_router, self.b_router, top, ids, weights, self.w_shared_gate, gate)
+        offsets = buf("offsets", (E + 1,), torch.int32)
+        order = buf("order", (P,), torch.int32)
+        moe.align(ids, E, offsets, order, flag)
+        # few rows per expert (decoding): narrow row tiles, so that a CTA does not multiply rows that do not exist
+        row_tile = 16 if P <= 16 * E else 64
+        gate_up = buf("gate_up", (P, 2 * ff), self.rt.dtype)
+        grouped.grouped_linear(x, self.w_gate_up, gate_up, rows=P, group_offsets=offsets, a_rows=order, a_row_div=top,
+                               row_tile=row_tile)
+        act = buf("act", (P, ff), self.rt.dtype)
+        ops.silu_mul(gate_up, act)
+        y = buf("y", (P, W), torch.float32)
+        grouped.grouped_linear(act, self.w_down, y, rows=P, group_offsets=offsets, c_rows=order, row_tile=row_tile)
+        shared = self.shared.forward(x, ctx) if self.shared is not None else None
+        out = buf("out", (T, W), torch.float32)
+        moe.combine(y, weights, out, shared=shared, gate=gate, col_scale=out_scale)
+        return out
