@@ -22,8 +22,27 @@ ops.register_signatures(SOURCE, {
 })
 
 
+MMA_SOURCE = "grouped_mma.cu"
+ops.register_signatures(MMA_SOURCE, {
+    "mlb_grouped_mma": [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong,
+                        c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_int, c_int,
+                        c_int, c_void_p],
+})
+
+# Tests set it to False to send bf16 products to the CUDA-core kernel and compare.
+USE_TENSOR_CORES = True
+
+
 def sources():
-    return [(SOURCE, {})]
+    return [(SOURCE, {}), (MMA_SOURCE, {})]
+
+
+def mma_supported(a: torch.Tensor, weight: torch.Tensor, a_group_cols: int = 0) -> bool:
+    """The tensor-core kernel moves 16-byte pieces: bf16 operands whose K, row pitches and column blocks are multiples
+    of 8 elements."""
+    return (USE_TENSOR_CORES and a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[2] % 8 == 0
+            and a.stride(0) % 8 == 0 and weight.stride(1) % 8 == 0 and weight.stride(0) % 8 == 0 and a_group_cols % 8 == 0
+            and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
 def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, rows: int, a_group_cols: int = 0,
@@ -52,9 +71,42 @@ def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, 
         ops._need(factor, "factor", torch.float32, 2)
         if factor.shape[1] < out.shape[1]:
             raise KernelError("grouped_linear: the factor matrix is narrower than the output")
+    if mma_supported(a, weight, a_group_cols):
+        L = ops.lib(MMA_SOURCE)
+        build.check(L, L.mlb_grouped_mma(
+            a.data_ptr(), a.stride(0), a_group_cols, weight.data_ptr(), weight.stride(1), weight.stride(0), out.data_ptr(),
+            out.stride(0), c_group_cols, ops._ptr(group_offsets), ops._ptr(a_rows), ops._ptr(c_rows), int(a_row_div),
+            ops._ptr(factor), factor.stride(0) if factor is not None else 0, 0, int(rows), N, K, G, ops.dtype_tag(out),
+            int(row_tile), ops._stream()))
+        return
     L = ops.lib(SOURCE)
     build.check(L, L.mlb_grouped_gemm(
         a.data_ptr(), a.stride(0), a_group_cols, weight.data_ptr(), weight.stride(1), weight.stride(0), out.data_ptr(),
         out.stride(0), c_group_cols, ops._ptr(group_offsets), ops._ptr(a_rows), ops._ptr(c_rows), int(a_row_div),
         ops._ptr(factor), factor.stride(0) if factor is not None else 0, int(rows), N, K, G, ops.dtype_tag(a),
         ops.dtype_tag(out), int(row_tile), ops._stream()))
+
+
+def grouped_silu_mul(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, rows: int, group_offsets: torch.Tensor,
+                     a_rows: Optional[torch.Tensor] = None, a_row_div: int = 1, row_tile: int = 64, alloc=None) -> None:
+    """weight [G, 2 * F, K]: per group F gate rows over F up rows; out[place] = silu(a gate^T) * (a up^T), [rows, F].
+    On the tensor cores both products and the activation are one kernel; otherwise the fused product leaves
+    [rows, 2 * F] (from `alloc(shape, dtype)`) and the activation kernel follows."""
+    ops._need(a, "a", dims=2); ops._need(weight, "weight", dims=3); ops._need(out, "out", dims=2)
+    G, two_f, K = weight.shape
+    F = two_f // 2
+    if two_f % 2 or tuple(out.shape) != (rows, F):
+        raise KernelError("grouped_silu_mul: the weight holds gate rows over up rows, the output one column per pair")
+    if mma_supported(a, weight):
+        ops._need(group_offsets, "group_offsets", torch.int32, 1)
+        if a_rows is not None:
+            ops._need(a_rows, "a_rows", torch.int32, 1)
+        L = ops.lib(MMA_SOURCE)
+        build.check(L, L.mlb_grouped_mma(
+            a.data_ptr(), a.stride(0), 0, weight.data_ptr(), weight.stride(1), weight.stride(0), out.data_ptr(), out.stride(0), 0,
+            group_offsets.data_ptr(), ops._ptr(a_rows), None, int(a_row_div), None, 0, F, int(rows), F, K, G,
+            ops.dtype_tag(out), int(row_tile), ops._stream()))
+        return
+    gate_up = alloc((rows, two_f), a.dtype) if alloc is not None else torch.empty((rows, two_f), dtype=a.dtype, device=a.device)
+    grouped_linear(a, weight, gate_up, rows=rows, group_offsets=group_offsets, a_rows=a_rows, a_row_div=a_row_div, row_tile=row_tile)
+    ops.silu_mul(gate_up, out)

@@ -151,7 +151,7 @@ def base_sources():
 def part_sources():
     """(source, defines) of the kernels that only some kinds of parts ask for (each part names its own in
     `kernel_sources`)."""
-    return [("residual.cu", {}), ("grouped_gemm.cu", {}), ("latent.cu", {}), ("moe.cu", {})]
+    return [("residual.cu", {}), ("grouped_gemm.cu", {}), ("grouped_mma.cu", {}), ("latent.cu", {}), ("moe.cu", {})]
 
 
 def all_sources():

@@ -16,7 +16,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..kernels import grouped, moe, ops
+from ..kernels import grouped, moe
 from .base import FEED_FORWARDS, FeedForward, Runtime, StepContext, WeightSpec, make, register_feed_forward, scratch
 
 
@@ -129,11 +129,9 @@ class RoutedExperts(FeedForward):
         moe.align(ids, E, offsets, order, flag)
         # few rows per expert (decoding): narrow row tiles, so that a CTA does not multiply rows that do not exist
         row_tile = 16 if P <= 16 * E else 64
-        gate_up = buf("gate_up", (P, 2 * ff), self.rt.dtype)
-        grouped.grouped_linear(x, self.w_gate_up, gate_up, rows=P, group_offsets=offsets, a_rows=order, a_row_div=top,
-                               row_tile=row_tile)
         act = buf("act", (P, ff), self.rt.dtype)
-        ops.silu_mul(gate_up, act)
+        grouped.grouped_silu_mul(x, self.w_gate_up, act, rows=P, group_offsets=offsets, a_rows=order, a_row_div=top,
+                                 row_tile=row_tile, alloc=lambda shape, dtype: buf("gate_up", shape, dtype))
         y = buf("y", (P, W), torch.float32)
         grouped.grouped_linear(act, self.w_down, y, rows=P, group_offsets=offsets, c_rows=order, row_tile=row_tile)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
