@@ -1,0 +1,298 @@
+// Latent attention on the tensor cores (mma.sync m16n8k16, bf16 operands, fp32 scores, weights and accumulation),
+// for prompt portions and decoded tokens alike.  Compiled per model: -DLAT_R (latent width) -DLAT_DR (rotated width).
+//
+// All heads read the same cache rows (see latent.cu): a query row is one (token, head) pair, and q [T*H, Dk] /
+// out [T*H, R] are plain row-major matrices with Dk = R + DR.  A CTA of four warps owns 16 consecutive query rows
+// of ONE sequence (a work item: sequence, first row among the sequence's new rows) and walks the keys those rows may
+// see in tiles of 32 at absolute multiples of 32, through a two-stage ring filled by cp.async straight from the pages.
+//   scores   each warp takes 8 of the tile's 32 keys: S[16 x 8] = Q[16 x Dk] K^T, Q and K by ldmatrix
+//   softmax  running maximum and sum per row in fp32; the warps meet in shared memory for the row's maximum and sum
+//   values   P[16 x 32] goes to shared memory as bf16; each warp owns a quarter of the R output columns and adds
+//            P V for them (V = the first R columns of the same cache rows, fetched with ldmatrix.trans)
+// A sink (one learned number per head) enters the denominator once, with no value.
+// With `splits` > 1 a work item's key tiles are divided among that many CTAs, which leave unnormalised partial
+// outputs with their maximum and sum in a workspace; latent_merge_kernel puts them together (and adds the sink).
+#include "common.cuh"
+
+#ifndef LAT_R
+#error "compile with -DLAT_R=<latent width> -DLAT_DR=<rotated width>"
+#endif
+
+using namespace mlb;
+
+MLB_DEFINE_LAST_ERROR()
+
+namespace {
+
+constexpr int R = LAT_R, DR = LAT_DR, DK = R + DR;
+constexpr int BM = 16, BN = 32, KP = DK + 8, PP = BN + 8;      // padded pitches in elements
+constexpr int WR = R / 4, NT = WR / 8;                          // output columns and n-tiles per warp
+static_assert(R % 32 == 0 && DK % 16 == 0, "latent width must be a multiple of 32, latent + rotated a multiple of 16");
+
+struct Params {
+    const __nv_bfloat16* q; const __nv_bfloat16* pages; __nv_bfloat16* out;
+    const float* sink;
+    const int* seq_starts; const int* seq_pos0; const int* block_table; const int* work;   // work: (sequence, first row) pairs
+    float* part_o; float* part_ml;         // [splits, rows, R] and [splits, rows, 2], rows = T * H
+    int max_blocks, num_pages, page_size, heads, window, splits, total_rows;
+    float scale;
+    int* error_flag;
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x2(unsigned (&r)[2], const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+struct Smem {
+    __nv_bfloat16 q[BM][KP];
+    __nv_bfloat16 k[2][BN][KP];
+    __nv_bfloat16 p[BM][PP];
+    float red_max[4][BM];
+    float red_sum[4][BM];
+};
+
+__global__ void __launch_bounds__(128)
+latent_mma_kernel(Params p) {
+    pdl_prologue();
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Smem& s = *reinterpret_cast<Smem*>(smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq = p.work[2 * blockIdx.x], first_row = p.work[2 * blockIdx.x + 1];
+    const int split = blockIdx.y;
+    const int H = p.heads;
+    const int seq_start = p.seq_starts[seq], n_new = p.seq_starts[seq + 1] - seq_start;
+    const int pos0 = p.seq_pos0[seq];
+    const int rows = min(BM, n_new * H - first_row);                       // rows of this tile that exist
+    const size_t row_base = (size_t)seq_start * H + first_row;             // global (token, head) row of the tile's first row
+    const int* table = p.block_table + (size_t)seq * p.max_blocks;
+
+    // what the tile's rows may see: from the first row's lower edge to the last row's own position
+    const int pos_first = pos0 + first_row / H, pos_last = pos0 + (first_row + rows - 1) / H;
+    const int lo_tile = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
+    const int tile_first = lo_tile / BN, tile_count_all = pos_last / BN - tile_first + 1;
+    const int t_begin = tile_first + (int)((long long)tile_count_all * split / p.splits);
+    const int t_end = tile_first + (int)((long long)tile_count_all * (split + 1) / p.splits);
+
+    // Q: the tile's rows, zeros behind the last one
+    for (int e = tid; e < BM * (DK / 8); e += 128) {
+        const int row = e / (DK / 8), piece = e % (DK / 8);
+        const bool ok = row < rows;
+        cp_async16(&s.q[row][piece * 8], ok ? (const void*)(p.q + (row_base + row) * DK + piece * 8) : (const void*)p.q, ok);
+    }
+    auto load_keys = [&](int stage, int tile) {
+        const int base = tile * BN;
+        for (int e = tid; e < BN * (DK / 8); e += 128) {
+            const int row = e / (DK / 8), piece = e % (DK / 8);
+            const int kp = base + row;
+            bool ok = kp >= lo_tile && kp <= pos_last;
+            const __nv_bfloat16* src = p.pages;
+            if (ok) {
+                const int block = kp / p.page_size;
+                const int page = block < p.max_blocks ? table[block] : -1;
+                if (page < 0 || page >= p.num_pages) {
+                    if (p.error_flag) atomicExch(p.error_flag, 2);
+                    ok = false;
+                } else {
+                    src = p.pages + ((size_t)page * p.page_size + kp % p.page_size) * DK + piece * 8;
+                }
+            }
+            cp_async16(&s.k[stage][row][piece * 8], src, ok);
+        }
+    };
+    if (t_begin < t_end) load_keys(0, t_begin);
+    cp_async_commit();
+
+    // this thread's two rows (lane / 4 and lane / 4 + 8): position and lower edge of each
+    int row_pos[2], row_lo[2];
+    float m_run[2], l_run[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = (lane >> 2) + 8 * h;
+        const bool exists = r < rows;
+        row_pos[h] = exists ? pos0 + (first_row + r) / H : -1;             // -1: sees nothing
+        row_lo[h] = (p.window > 0 && row_pos[h] - p.window + 1 > 0) ? row_pos[h] - p.window + 1 : 0;
+        const bool own_sink = p.sink != nullptr && p.splits == 1 && exists;
+        m_run[h] = own_sink ? p.sink[(first_row + r) % H] : -INFINITY;
+        l_run[h] = own_sink ? 1.0f : 0.0f;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
+
+    const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
+    for (int tile = t_begin; tile < t_end; ++tile) {
+        const int stage = (tile - t_begin) & 1;
+        cp_async_wait<0>();
+        __syncthreads();                                    // this tile's keys (and Q) have landed; the other stage is free
+        if (tile + 1 < t_end) load_keys(stage ^ 1, tile + 1);
+        cp_async_commit();
+        // ---- scores of this warp's 8 keys
+        float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int ks = 0; ks < DK / 16; ++ks) {
+            unsigned a[4], b[2];
+            ldmatrix_x4(a, &s.q[a_row][ks * 16 + a_col]);
+            ldmatrix_x2(b, &s.k[stage][warp * 8 + (lane & 7)][ks * 16 + 8 * ((lane >> 3) & 1)]);
+            mma_bf16(sc, a, b[0], b[1]);
+        }
+        const int key0 = tile * BN + warp * 8 + 2 * (lane & 3);
+        float part_max[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int kp = key0 + i;
+                const bool seen = kp <= row_pos[h] && kp >= row_lo[h];
+                sc[2 * h + i] = seen ? sc[2 * h + i] * p.scale : -INFINITY;
+            }
+            float v = fmaxf(sc[2 * h], sc[2 * h + 1]);
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+            part_max[h] = v;
+        }
+        if ((lane & 3) == 0) { s.red_max[warp][lane >> 2] = part_max[0]; s.red_max[warp][(lane >> 2) + 8] = part_max[1]; }
+        __syncthreads();
+        float corr[2], part_sum[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = (lane >> 2) + 8 * h;
+            const float m_new = fmaxf(fmaxf(fmaxf(s.red_max[0][r], s.red_max[1][r]), fmaxf(s.red_max[2][r], s.red_max[3][r])), m_run[h]);
+            corr[h] = (m_run[h] == -INFINITY) ? 0.0f : expf(m_run[h] - m_new);      // m_new >= m_run; both -inf: nothing seen yet
+            const float p0 = sc[2 * h] == -INFINITY ? 0.0f : expf(sc[2 * h] - m_new);
+            const float p1 = sc[2 * h + 1] == -INFINITY ? 0.0f : expf(sc[2 * h + 1] - m_new);
+            m_run[h] = m_new;
+            *reinterpret_cast<__nv_bfloat162*>(&s.p[r][warp * 8 + 2 * (lane & 3)]) = __floats2bfloat162_rn(p0, p1);
+            float v = p0 + p1;
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            part_sum[h] = v;
+        }
+        if ((lane & 3) == 0) { s.red_sum[warp][lane >> 2] = part_sum[0]; s.red_sum[warp][(lane >> 2) + 8] = part_sum[1]; }
+        __syncthreads();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = (lane >> 2) + 8 * h;
+            l_run[h] = l_run[h] * corr[h] + ((s.red_sum[0][r] + s.red_sum[1][r]) + (s.red_sum[2][r] + s.red_sum[3][r]));
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) { acc[j][0] *= corr[0]; acc[j][1] *= corr[0]; acc[j][2] *= corr[1]; acc[j][3] *= corr[1]; }
+        // ---- this warp's quarter of the output columns: acc += P V
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks) {
+            unsigned a[4];
+            ldmatrix_x4(a, &s.p[a_row][ks * 16 + a_col]);
+#pragma unroll
+            for (int j = 0; j < NT; j += 2) {
+                unsigned v[4];
+                ldmatrix_x4_trans(v, &s.k[stage][ks * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][warp * WR + j * 8 + 8 * (lane >> 4)]);
+                mma_bf16(acc[j], a, v[0], v[1]);
+                if (j + 1 < NT) mma_bf16(acc[j + 1], a, v[2], v[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    // ---- results
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = (lane >> 2) + 8 * h;
+        if (r >= rows) continue;
+        const size_t g = row_base + r;
+        if (p.splits == 1) {
+            const float inv = l_run[h] > 0.0f ? 1.0f / l_run[h] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int c = warp * WR + j * 8 + 2 * (lane & 3);
+                *reinterpret_cast<__nv_bfloat162*>(p.out + g * R + c) = __floats2bfloat162_rn(acc[j][2 * h] * inv, acc[j][2 * h + 1] * inv);
+            }
+        } else {
+            float* o = p.part_o + ((size_t)split * p.total_rows + g) * R;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int c = warp * WR + j * 8 + 2 * (lane & 3);
+                *reinterpret_cast<float2*>(o + c) = make_float2(acc[j][2 * h], acc[j][2 * h + 1]);
+            }
+            if (warp == 0 && (lane & 3) == 0) {
+                float* ml = p.part_ml + ((size_t)split * p.total_rows + g) * 2;
+                ml[0] = m_run[h]; ml[1] = l_run[h];
+            }
+        }
+    }
+}
+
+// out[g, :] = sum_s O_s e^(m_s - m) / (sum_s l_s e^(m_s - m) + e^(sink - m)),  m = max(m_s, sink); splits in order
+__global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ sink,
+                                    __nv_bfloat16* __restrict__ out, int splits, int total_rows, int heads) {
+    pdl_prologue();
+    const int g = blockIdx.x;
+    float m = sink ? sink[g % heads] : -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((size_t)s * total_rows + g) * 2]);
+    float l = sink ? expf(sink[g % heads] - m) : 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = part_ml[((size_t)s * total_rows + g) * 2];
+        if (ms != -INFINITY) l += part_ml[((size_t)s * total_rows + g) * 2 + 1] * expf(ms - m);
+    }
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float o = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[((size_t)s * total_rows + g) * 2];
+            if (ms != -INFINITY) o += part_o[((size_t)s * total_rows + g) * R + c] * expf(ms - m);
+        }
+        out[(size_t)g * R + c] = __float2bfloat16_rn(o * inv);
+    }
+}
+
+}  // namespace
+
+MLB_EXPORT int mlb_latent_mma_widths(int which) { return which == 0 ? R : DR; }
+
+// q [T*H, R+DR] bf16, pages [num_pages, page_size, R+DR] bf16, out [T*H, R] bf16.  work: num_work (sequence, first row)
+// pairs, each a tile of up to 16 (token, head) rows of one sequence.  splits > 1 needs part_o [splits, T*H, R] and
+// part_ml [splits, T*H, 2] fp32.
+MLB_EXPORT int mlb_latent_attention_mma(const void* q, const void* pages, void* out, const float* sink, const int* seq_starts,
+                                        const int* seq_pos0, const int* block_table, const int* work, int num_work,
+                                        float* part_o, float* part_ml, int max_blocks, int num_pages, int page_size,
+                                        int heads, int window, int splits, int total_rows, float scale, int* error_flag,
+                                        cudaStream_t stream) {
+    if (num_work < 0 || heads <= 0 || splits < 1 || splits > 65535 || total_rows < 0 || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0)
+        return fail(MLB_INVALID_ARGUMENT, "latent_attention_mma: bad sizes");
+    if (splits > 1 && (!part_o || !part_ml)) return fail(MLB_INVALID_ARGUMENT, "latent_attention_mma: split keys need a workspace");
+    if (num_work == 0) return MLB_OK;
+    static bool configured[MAX_DEVICES] = {false};
+    const size_t smem = sizeof(Smem);
+    if (!configured[device_index()]) {
+        if (cudaFuncSetAttribute(latent_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return fail(MLB_UNSUPPORTED_SIZE, "latent_attention_mma: %zu bytes of shared memory per CTA are not available", smem);
+        configured[device_index()] = true;
+    }
+    Params p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, sink, seq_starts, seq_pos0, block_table, work,
+             part_o, part_ml, max_blocks, num_pages, page_size, heads, window, splits, total_rows, scale, error_flag};
+    launch_kernel(latent_mma_kernel, dim3(num_work, splits), 128, smem, stream, p);
+    int status = check_launch("latent_attention_mma");
+    if (status != MLB_OK || splits == 1) return status;
+    launch_kernel(latent_merge_kernel, total_rows, 128, 0, stream, (const float*)part_o, (const float*)part_ml, sink,
+                  (__nv_bfloat16*)out, splits, total_rows, heads);
+    return check_launch("latent_merge");
+}

@@ -161,8 +161,9 @@ def all_sources():
     out = base_sources()
     for d in (32, 64, 128):
         out += attention.mma_sources(d) + attention.tc_sources(d)
-    from . import gemm_bf16
-    return out + gemm_bf16.sources() + [("gemv_noalloc.cu", {})] + part_sources()
+    from . import gemm_bf16, latent
+    return (out + gemm_bf16.sources() + [("gemv_noalloc.cu", {})] + part_sources()
+            + latent.mma_sources(64, 32) + latent.mma_sources(512, 64))
 
 
 # ------------------------------------------------------------------------------ basic

@@ -87,7 +87,7 @@ class LatentAttention(Mixer):
 
     def kernel_sources(self):
         own = latent.sources() + grouped.sources()
-        return own if self.rt.is_fp32 else own + gemm_bf16.sources(engine_only=True)
+        return own if self.rt.is_fp32 else own + latent.mma_sources(self.rank, self.rot_dim) + gemm_bf16.sources(engine_only=True)
 
     def bind(self, tensors):
         n = self.names
@@ -111,6 +111,16 @@ class LatentAttention(Mixer):
     def own_tensors(self):
         return [self.w_in, self.w_uk_t, self.w_uv, self.w_o, self.kv_norm, self.sink, self.inv_freq]
 
+    # --- launch plans frozen into a captured decode step ----------------------------------
+    def plan_stale(self, ctx: StepContext, max_seq_len: int) -> bool:
+        return latent.plan_stale(ctx, max_seq_len)
+
+    def forget_plans(self, ctx: StepContext) -> None:
+        latent.forget_plans(ctx)
+
+    def plan_group(self):
+        return ("latent_attention", self.rt.device)
+
     # --- compute ------------------------------------------------------------------------
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
         T, H, dt = x.shape[0], self.heads, self.rt.dtype
@@ -130,8 +140,8 @@ class LatentAttention(Mixer):
         grouped.grouped_linear(q_plain, self.w_uk_t, q_full, rows=T, a_group_cols=self.dim, c_group_cols=self.kv_width,
                                row_tile=row_tile)
         o_latent = ctx.buffer("latent.o_latent", (T, H * self.rank), dt)
-        latent.attention_plain(q_full, cache.pages, o_latent, self.sink, ctx.positions, ctx.token_seq, cache.block_table,
-                               H, self.rank, self.rot_dim, self.scale, self.window, flag)
+        latent.attention(q_full, cache.pages, o_latent, self.sink, ctx, cache.block_table, H, self.rank, self.rot_dim,
+                         self.scale, self.window)
         # o_h = Wuv_h (sum_j p_j c_j), times the gate
         o = ctx.buffer("latent.o", (T, H * self.vdim), dt)
         grouped.grouped_linear(o_latent, self.w_uv, o, rows=T, a_group_cols=self.rank, c_group_cols=self.vdim, factor=gate,

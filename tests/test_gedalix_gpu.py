@@ -252,6 +252,27 @@ def test_mixed_batches_over_a_tight_pool(folders, key, dtype):
     assert pool.total_allocations > pool.num_pages, "the pool was never tight enough to use a page again"
 
 
+@pytest.mark.parametrize("key", ["c", "d"])
+def test_tensor_core_attention_and_products_track_the_plain_kernels(folders, key):
+    """bf16, the same schedule twice: on the tensor-core kernels (attention with key splits in the decoded tail, grouped
+    products) and on the plain ones.  Tiles of 16 (token, head) rows span several tokens here (two and four heads)."""
+    from microllm_rocm_b200.kernels import grouped, latent
+    folder, raw, weights = folders[key]
+    assert latent.mma_supported(raw["layers"][0]["mixer"]["kv_rank"], raw["layers"][0]["mixer"]["rot_dim"])
+    reqs = requests_for(raw, [3, 50, 290], seed=2)
+    steps, peak = steps_mixed(reqs, max_live=3, seed=5, decode_tail=20)
+    fast = collect(engine_for(folder, "bfloat16", max_tokens=peak), steps)
+    latent.USE_TENSOR_CORES = grouped.USE_TENSOR_CORES = False
+    try:
+        slow = collect(engine_for(folder, "bfloat16", max_tokens=peak), steps)
+    finally:
+        latent.USE_TENSOR_CORES = grouped.USE_TENSOR_CORES = True
+    compare(fast, key, raw, weights, reqs, "bfloat16")
+    compare(slow, key, raw, weights, reqs, "bfloat16")
+    far = [k for k in fast if float((fast[k] - slow[k]).abs().max()) > 0.03 * float(slow[k].abs().max())]
+    assert len(far) <= len(fast) // 25, f"{len(far)} of {len(fast)} positions differ between the kernels"
+
+
 def test_fp32_does_not_depend_on_cuts_batches_or_pages(folders):
     folder, raw, weights = folders["a"]
     reqs = requests_for(raw, [70, 133, 20, 45], seed=4)
