@@ -2,7 +2,8 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
                     [--model PRESET] [--batch B] [--prompt P] [--context C]
-                    [--workload decode|mixed] [--requests R] [--new-tokens N] [--chunk T]
+                    [--workload decode|mixed|designs] [--requests R] [--new-tokens N] [--chunk T]
+                    [--size NAME] [--kernels]
 
 The model has the layer sizes of the Qwen2.5-1.5B shape (BASELINE.json configs[2]) with
 random bf16 weights; the default run decodes a batch of 8 requests that hold 2,048-token
@@ -294,6 +295,120 @@ def step_timeline(session):
         row[2] += exposed
     span = records[-1][2] - records[0][1] if records else 0.0
     return span, sorted(rows.items(), key=lambda kv: -kv[1][2])
+
+
+# ---------------------------------------------------------------------------------- two designs side by side
+# `--workload designs`: the Gedalix decoder (latent attention, routed experts) beside the Qwen2 dense decoder at equal
+# size: the same width, layers, heads, vocabulary, and a dense feed-forward as wide as what a Gedalix token runs
+# (its chosen experts plus the shared one).  Random weights, bf16.  Per design: one prompt step of --prefill-tokens
+# tokens, captured decode steps of --batch requests at context --prompt, and the kernels of one step of each kind
+# with their summed durations (for the comparison of like kernels).
+DESIGN_SIZES = {
+    "small": dict(gedalix="gedalix-small", layers=4),
+    "16b-layers": dict(gedalix="gedalix-16b-layers", layers=4),
+}
+
+
+def _equal_dense(raw, layers):
+    from microllm_rocm_b200.config import Qwen2Config
+    layer = raw["layers"][0]
+    m, mlp = layer["mixer"], layer["mlp"]
+    inter = mlp["router"]["top"] * mlp["expert"]["ff"] + (mlp["shared"]["ff"] if mlp.get("shared") else 0)
+    return Qwen2Config.from_dict(dict(vocab_size=raw["vocab"], hidden_size=raw["width"], num_hidden_layers=layers,
+                                      num_attention_heads=m["heads"], num_key_value_heads=max(1, m["heads"] // 8), head_dim=m["dim"],
+                                      intermediate_size=inter, max_position_embeddings=raw["max_positions"], rope_theta=1e6,
+                                      rms_norm_eps=1e-6, tie_word_embeddings=False))
+
+
+def _kernel_rows(step_fn, repeats=3):
+    """(name, launches, summed duration in us, summed exposed time in us: see _exposed) of one call of step_fn, the
+    kernels that add most to the step first.  Kernels start early behind their predecessors, so a duration holds
+    the wait for the predecessor too; the exposed times add up to the step."""
+    class _S:
+        def step(self_inner):
+            step_fn()
+    records = _kernel_records(_S(), repeats)
+    per = len(records) // repeats
+    rows = {}
+    for name, duration, exposed in _exposed(records[per:2 * per]):
+        short = name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0].split("<")[0]
+        row = rows.setdefault(short, [0, 0.0, 0.0])
+        row[0] += 1
+        row[1] += duration
+        row[2] += exposed
+    return [(n, c, round(d, 1), round(e, 1)) for n, (c, d, e) in sorted(rows.items(), key=lambda kv: -kv[1][2])][:14]
+
+
+def run_designs(args):
+    import copy
+
+    import torch
+
+    from microllm_rocm_b200.config import GedalixConfig
+    from microllm_rocm_b200.config.gedalix import PRESETS as GEDALIX_PRESETS
+    from microllm_rocm_b200.engine.loading import random_engine
+    from microllm_rocm_b200.engine.step import StepEntry
+    names = [args.size] if args.size else list(DESIGN_SIZES)
+    out = {"workload": "designs", "dtype": "bf16", "data": "synthetic", "prefill_tokens": args.prefill_tokens, "batch": args.batch,
+           "context": args.prompt, "sizes": {}}
+    gen = torch.Generator().manual_seed(0)
+    for name in names:
+        size = DESIGN_SIZES[name]
+        raw = copy.deepcopy(GEDALIX_PRESETS[size["gedalix"]])
+        layers = args.layers or size["layers"]
+        raw["layers"] = raw["layers"][:layers]
+        raw["max_positions"] = max(raw["max_positions"], args.prompt + 512)
+        designs = {"gedalix": GedalixConfig.from_dict(raw), "qwen2": _equal_dense(raw, layers)}
+        result = {}
+        for design, cfg in designs.items():
+            page = 64
+            engine = random_engine(cfg, seed=0, dtype="bfloat16", page_size=page, max_tokens=(args.batch + 1) * (args.prompt + 512),
+                                   max_requests=args.batch + 1, draw_on_device=True)
+            vocab = cfg.vocab_size
+
+            def prefill_once():
+                engine.cache.add("pf")
+                toks = torch.randint(0, vocab, (args.prefill_tokens,), generator=gen).tolist()
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                start.record()
+                engine.step([StepEntry("pf", toks, [len(toks) - 1])])
+                end.record()
+                torch.cuda.synchronize()
+                engine.cache.release("pf")
+                return start.elapsed_time(end)
+
+            for _ in range(3):
+                prefill_once()
+            prefill_ms = statistics.median([prefill_once() for _ in range(5)])
+            prefill_kernels = _kernel_rows(prefill_once) if args.kernels else None
+            prompts = [torch.randint(0, vocab, (args.prompt,), generator=gen).tolist() for _ in range(args.batch)]
+            session = DecodeSession(engine, prompts, args.warmup + args.steps + 16)
+            for _ in range(args.warmup):
+                session.step()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(args.steps):
+                session.step()
+            end.record()
+            torch.cuda.synchronize()
+            decode_ms = start.elapsed_time(end) / args.steps
+            decode_kernels = _kernel_rows(session.step) if args.kernels else None
+            session.close()
+            engine.check_device_errors()
+            result[design] = {"parameters": engine.parameter_count, "prefill_ms": round(prefill_ms, 3),
+                              "prefill_tokens_per_s": round(args.prefill_tokens / prefill_ms * 1e3),
+                              "decode_ms_per_step": round(decode_ms, 4), "decode_tokens_per_s": round(args.batch / decode_ms * 1e3),
+                              "captured": session.graph is not None}
+            if args.kernels:
+                result[design]["prefill_kernels"] = prefill_kernels
+                result[design]["decode_kernels"] = decode_kernels
+            del engine, session
+            torch.cuda.empty_cache()
+        out["sizes"][name] = {"layers": layers, **result}
+    print(json.dumps(out))
+    return 0
 
 
 def run_mixed(args):
@@ -589,7 +704,9 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "prefill-timeline"],
                     help="run just one timed part and print a short line (for profiler captures)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "designs"])
+    ap.add_argument("--size", default="", help="designs: one of the sizes (default: all)")
+    ap.add_argument("--kernels", action="store_true", help="designs: list the kernels of a prompt step and of a decode step")
     ap.add_argument("--requests", type=int, default=64, help="mixed: how many requests")
     ap.add_argument("--min-prompt", type=int, default=128)
     ap.add_argument("--max-prompt", type=int, default=2048)
@@ -608,6 +725,8 @@ def main():
         args.warmup = 3
     if args.workload == "mixed":
         return run_mixed(args)
+    if args.workload == "designs":
+        return run_designs(args)
     return run_ours(args)
 
 

@@ -21,6 +21,7 @@ MLB_DEFINE_LAST_ERROR()
 namespace {
 
 constexpr int BN = 64, BK = 16, TN = 4;
+constexpr int MAX_GROUPS = 1024;       // with a list of offsets (the offsets travel through shared memory)
 
 struct GroupedParams {
     const void* A; long long lda; long long a_group_cols;
@@ -44,7 +45,12 @@ grouped_gemm_kernel(GroupedParams p) {
     __shared__ int src_row[BM];
     __shared__ int dst_row[BM];
     __shared__ int tile_info[3];             // group, first place, places in this tile
+    __shared__ int offsets_s[MAX_GROUPS + 1];
     const int tid = threadIdx.x;
+    if (p.group_offsets) {
+        for (int g = tid; g <= p.G; g += blockDim.x) offsets_s[g] = p.group_offsets[g];
+        __syncthreads();
+    }
     if (tid == 0) {
         int group = -1, first = 0, count = 0;
         if (p.group_offsets == nullptr) {
@@ -56,7 +62,7 @@ grouped_gemm_kernel(GroupedParams p) {
         } else {
             int tile = blockIdx.y;
             for (int g = 0; g < p.G; ++g) {
-                const int lo = p.group_offsets[g], n = p.group_offsets[g + 1] - lo;
+                const int lo = offsets_s[g], n = offsets_s[g + 1] - lo;
                 const int tiles = (n + BM - 1) / BM;
                 if (tile < tiles) { group = g; first = lo + tile * BM; count = min(BM, n - tile * BM); break; }
                 tile -= tiles;
@@ -152,6 +158,7 @@ MLB_EXPORT int mlb_grouped_gemm(const void* A, long long lda, long long a_group_
                                 int row_tile, cudaStream_t stream) {
     if (M < 0 || N <= 0 || K <= 0 || G <= 0 || a_row_div <= 0 || (row_tile != 16 && row_tile != 64))
         return fail(MLB_INVALID_ARGUMENT, "grouped_gemm: bad sizes M=%d N=%d K=%d G=%d", M, N, K, G);
+    if (group_offsets && G > MAX_GROUPS) return fail(MLB_UNSUPPORTED_SIZE, "grouped_gemm: more than %d groups", MAX_GROUPS);
     if (M == 0) return MLB_OK;
     GroupedParams p{A, lda, a_group_cols, W, ldw, w_group_stride, C, ldc, c_group_cols, group_offsets, a_rows, c_rows,
                     a_row_div, factor, ldf, M, N, K, G};

@@ -3,7 +3,7 @@
 //
 //     C[c_row(r), g * c_group_cols + n] = epilogue( sum_k A[a_row(r), g * a_group_cols + k] * W[g][n, k] )
 //
-// A CTA owns a tile of BM rows (64, or 16 when groups hold few rows) of ONE group by 64 output columns, and walks K in
+// A CTA owns a tile of BM rows (128 or 64, or 16 when groups hold few rows) of ONE group by 64 output columns, and walks K in
 // steps of 32 through a three-stage ring filled with cp.async (16-byte pieces: rows of A are gathered through the
 // row list on the way in).  Fragments come out of shared memory with ldmatrix; rows of the ring are padded to 80
 // bytes, which keeps the eight rows of an ldmatrix phase in different banks.
@@ -21,6 +21,7 @@ MLB_DEFINE_LAST_ERROR()
 namespace {
 
 constexpr int BN = 64, BK = 32, STAGES = 3, PITCH = BK + 8;     // elements per padded row of the ring
+constexpr int MAX_GROUPS = 1024;       // with a list of offsets (the offsets travel through shared memory)
 
 struct MmaParams {
     const __nv_bfloat16* A; long long lda; long long a_group_cols;
@@ -51,21 +52,36 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
 }
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + expf(-g)); }
 
+__host__ __device__ constexpr int threads_of(int bm) { return 128; }
+constexpr size_t smem_of(int bm, bool dual) {
+    return (size_t)STAGES * (bm + (dual ? 2 : 1) * BN) * PITCH * sizeof(__nv_bfloat16) + (2 * bm + 4 + MAX_GROUPS + 1) * sizeof(int);
+}
+
 template <typename OutT, int BM, bool DUAL>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(threads_of(BM))
 grouped_mma_kernel(MmaParams p) {
-    constexpr int WARPS_M = BM / 16;                 // 4 (BM 64) or 1 (BM 16)
+    constexpr int THREADS = threads_of(BM);
+    constexpr int WARPS_M = BM >= 64 ? 4 : 1;        // BM 128 and 64: four warps under one another; BM 16: side by side
+    constexpr int MT = BM / (16 * WARPS_M);          // 16-row tiles per warp: 2 (BM 128: a weight fragment serves both) or 1
     constexpr int WARPS_N = 4 / WARPS_M;             // 1 or 4
     constexpr int WN = BN / WARPS_N;                 // columns per warp: 64 or 16
     constexpr int NT = WN / 8;                       // n-tiles per warp: 8 or 2
     constexpr int NB = DUAL ? 2 : 1;
     pdl_prologue();
-    __shared__ __align__(16) __nv_bfloat16 As[STAGES][BM][PITCH];
-    __shared__ __align__(16) __nv_bfloat16 Ws[STAGES][NB][BN][PITCH];
-    __shared__ int src_row[BM];
-    __shared__ int dst_row[BM];
-    __shared__ int tile_info[3];
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    typedef __nv_bfloat16 (*ATile)[BM][PITCH];
+    typedef __nv_bfloat16 (*WTile)[NB][BN][PITCH];
+    ATile As = reinterpret_cast<ATile>(smem_raw);                                                   // [STAGES][BM][PITCH]
+    WTile Ws = reinterpret_cast<WTile>(smem_raw + (size_t)STAGES * BM * PITCH * sizeof(__nv_bfloat16));   // [STAGES][NB][BN][PITCH]
+    int* src_row = reinterpret_cast<int*>(smem_raw + (size_t)STAGES * (BM + NB * BN) * PITCH * sizeof(__nv_bfloat16));
+    int* dst_row = src_row + BM;
+    int* tile_info = dst_row + BM;
+    int* offsets_s = tile_info + 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (p.group_offsets) {                           // fetched by all threads at once, walked by one
+        for (int g = tid; g <= p.G; g += blockDim.x) offsets_s[g] = p.group_offsets[g];
+        __syncthreads();
+    }
     if (tid == 0) {
         int group = -1, first = 0, count = 0;
         if (p.group_offsets == nullptr) {
@@ -77,7 +93,7 @@ grouped_mma_kernel(MmaParams p) {
         } else {
             int tile = blockIdx.y;
             for (int g = 0; g < p.G; ++g) {
-                const int lo = p.group_offsets[g], n = p.group_offsets[g + 1] - lo;
+                const int lo = offsets_s[g], n = offsets_s[g + 1] - lo;
                 const int tiles = (n + BM - 1) / BM;
                 if (tile < tiles) { group = g; first = lo + tile * BM; count = min(BM, n - tile * BM); break; }
                 tile -= tiles;
@@ -106,7 +122,7 @@ grouped_mma_kernel(MmaParams p) {
     auto load_stage = [&](int stage, int kt) {
         const int k0 = kt * BK;
         // A: BM rows x 4 pieces of 8 elements
-        for (int e = tid; e < BM * 4; e += 128) {
+        for (int e = tid; e < BM * 4; e += THREADS) {
             const int row = e >> 2, piece = e & 3, k = k0 + piece * 8;
             const int a = src_row[row];
             const bool ok = a >= 0 && k < p.K;
@@ -114,7 +130,7 @@ grouped_mma_kernel(MmaParams p) {
         }
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
-            for (int e = tid; e < BN * 4; e += 128) {
+            for (int e = tid; e < BN * 4; e += THREADS) {
                 const int row = e >> 2, piece = e & 3, k = k0 + piece * 8;
                 const int n = n0 + row;
                 const bool ok = n < p.N && k < p.K;
@@ -124,13 +140,15 @@ grouped_mma_kernel(MmaParams p) {
         }
     };
 
-    float acc[NB][NT][4];
+    float acc[MT][NB][NT][4];
 #pragma unroll
-    for (int b = 0; b < NB; ++b)
+    for (int m = 0; m < MT; ++m)
 #pragma unroll
-        for (int j = 0; j < NT; ++j)
+        for (int b = 0; b < NB; ++b)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[b][j][i] = 0.0f;
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[m][b][j][i] = 0.0f;
 
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
@@ -138,7 +156,7 @@ grouped_mma_kernel(MmaParams p) {
         cp_async_commit();
     }
     const int warp_m = warp % WARPS_M, warp_n = warp / WARPS_M;
-    const int a_row = warp_m * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
+    const int a_row = warp_m * 16 * MT + (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
     const int b_row = (lane & 7) + 8 * (lane >> 4), b_col = 8 * ((lane >> 3) & 1);
     for (int kt = 0; kt < k_tiles; ++kt) {
         cp_async_wait<STAGES - 2>();
@@ -148,24 +166,30 @@ grouped_mma_kernel(MmaParams p) {
         const int stage = kt % STAGES;
 #pragma unroll
         for (int ks = 0; ks < BK / 16; ++ks) {
-            unsigned a[4];
-            ldmatrix_x4(a, &As[stage][a_row][ks * 16 + a_col]);
+            unsigned a[MT][4];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) ldmatrix_x4(a[m], &As[stage][a_row + 16 * m][ks * 16 + a_col]);
 #pragma unroll
             for (int b = 0; b < NB; ++b)
 #pragma unroll
                 for (int j = 0; j < NT; j += 2) {
                     unsigned w[4];
                     ldmatrix_x4(w, &Ws[stage][b][warp_n * WN + j * 8 + b_row][ks * 16 + b_col]);
-                    mma_bf16(acc[b][j], a, w[0], w[1]);
-                    mma_bf16(acc[b][j + 1], a, w[2], w[3]);
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        mma_bf16(acc[m][b][j], a[m], w[0], w[1]);
+                        mma_bf16(acc[m][b][j + 1], a[m], w[2], w[3]);
+                    }
                 }
         }
     }
     cp_async_wait<0>();
     // accumulator element i of n-tile j: row (lane / 4) + 8 * (i / 2), column 2 * (lane % 4) + (i % 2)
 #pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
     for (int half = 0; half < 2; ++half) {
-        const int c = dst_row[warp_m * 16 + (lane >> 2) + 8 * half];
+        const int c = dst_row[warp_m * 16 * MT + 16 * m + (lane >> 2) + 8 * half];
         if (c < 0) continue;
 #pragma unroll
         for (int j = 0; j < NT; ++j)
@@ -174,19 +198,31 @@ grouped_mma_kernel(MmaParams p) {
                 const int n = n0 + warp_n * WN + j * 8 + 2 * (lane & 3) + i;
                 if (n >= p.N) continue;
                 const size_t col = (size_t)group * p.c_group_cols + n;
-                float v = acc[0][j][half * 2 + i];
-                if (DUAL) v = silu(v) * acc[NB - 1][j][half * 2 + i];
+                float v = acc[m][0][j][half * 2 + i];
+                if (DUAL) v = silu(v) * acc[m][NB - 1][j][half * 2 + i];
                 if (p.factor) v *= p.factor[(size_t)c * p.ldf + col];
                 ((OutT*)p.C)[(size_t)c * p.ldc + col] = from_f32<OutT>(v);
             }
     }
 }
 
+template <typename OutT, int BM, bool DUAL>
+void launch_tile(const MmaParams& p, dim3 grid, cudaStream_t stream) {
+    static bool configured[MAX_DEVICES] = {false};               // the larger tiles need more shared memory than the default limit
+    constexpr size_t smem = smem_of(BM, DUAL);
+    if (smem > 48 * 1024 && !configured[device_index()]) {
+        cudaFuncSetAttribute(grouped_mma_kernel<OutT, BM, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        configured[device_index()] = true;
+    }
+    launch_kernel(grouped_mma_kernel<OutT, BM, DUAL>, grid, threads_of(BM), smem, stream, p);
+}
+
 template <typename OutT, bool DUAL>
 void launch(const MmaParams& p, int row_tile, unsigned tiles_y, cudaStream_t stream) {
     dim3 grid((p.N + BN - 1) / BN, tiles_y);
-    if (row_tile == 16) launch_kernel(grouped_mma_kernel<OutT, 16, DUAL>, grid, 128, 0, stream, p);
-    else launch_kernel(grouped_mma_kernel<OutT, 64, DUAL>, grid, 128, 0, stream, p);
+    if (row_tile == 16) launch_tile<OutT, 16, DUAL>(p, grid, stream);
+    else if (row_tile == 64) launch_tile<OutT, 64, DUAL>(p, grid, stream);
+    else launch_tile<OutT, 128, DUAL>(p, grid, stream);
 }
 
 }  // namespace
@@ -197,10 +233,11 @@ MLB_EXPORT int mlb_grouped_mma(const void* A, long long lda, long long a_group_c
                                const int* group_offsets, const int* a_rows, const int* c_rows, int a_row_div,
                                const float* factor, long long ldf, long long dual_rows, int M, int N, int K, int G,
                                int out_dtype, int row_tile, cudaStream_t stream) {
-    if (M < 0 || N <= 0 || K <= 0 || G <= 0 || a_row_div <= 0 || dual_rows < 0 || (row_tile != 16 && row_tile != 64))
+    if (M < 0 || N <= 0 || K <= 0 || G <= 0 || a_row_div <= 0 || dual_rows < 0 || (row_tile != 16 && row_tile != 64 && row_tile != 128))
         return fail(MLB_INVALID_ARGUMENT, "grouped_mma: bad sizes M=%d N=%d K=%d G=%d", M, N, K, G);
     if (K % 8 || lda % 8 || ldw % 8 || a_group_cols % 8 || w_group_stride % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16)
         return fail(MLB_UNSUPPORTED_SIZE, "grouped_mma: K, the row pitches and the column blocks must be multiples of 8 elements");
+    if (group_offsets && G > MAX_GROUPS) return fail(MLB_UNSUPPORTED_SIZE, "grouped_mma: more than %d groups", MAX_GROUPS);
     if (M == 0) return MLB_OK;
     MmaParams p{(const __nv_bfloat16*)A, lda, a_group_cols, (const __nv_bfloat16*)W, ldw, w_group_stride, C, ldc, c_group_cols,
                 group_offsets, a_rows, c_rows, a_row_div, factor, ldf, dual_rows, M, N, K, G};

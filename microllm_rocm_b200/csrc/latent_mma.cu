@@ -27,6 +27,7 @@ namespace {
 constexpr int R = LAT_R, DR = LAT_DR, DK = R + DR;
 constexpr int BM = 16, BN = 32, KP = DK + 8, PP = BN + 8;      // padded pitches in elements
 constexpr int WR = R / 4, NT = WR / 8;                          // output columns and n-tiles per warp
+static_assert(BN * 4 == 128, "four threads per cache row of a key tile");
 static_assert(R % 32 == 0 && DK % 16 == 0, "latent width must be a multiple of 32, latent + rotated a multiple of 16");
 
 struct Params {
@@ -99,25 +100,25 @@ latent_mma_kernel(Params p) {
         const bool ok = row < rows;
         cp_async16(&s.q[row][piece * 8], ok ? (const void*)(p.q + (row_base + row) * DK + piece * 8) : (const void*)p.q, ok);
     }
+    // Four threads share a cache row: each looks the row's page up ONCE per tile and copies every fourth 16-byte piece.
     auto load_keys = [&](int stage, int tile) {
-        const int base = tile * BN;
-        for (int e = tid; e < BN * (DK / 8); e += 128) {
-            const int row = e / (DK / 8), piece = e % (DK / 8);
-            const int kp = base + row;
-            bool ok = kp >= lo_tile && kp <= pos_last;
-            const __nv_bfloat16* src = p.pages;
-            if (ok) {
-                const int block = kp / p.page_size;
-                const int page = block < p.max_blocks ? table[block] : -1;
-                if (page < 0 || page >= p.num_pages) {
-                    if (p.error_flag) atomicExch(p.error_flag, 2);
-                    ok = false;
-                } else {
-                    src = p.pages + ((size_t)page * p.page_size + kp % p.page_size) * DK + piece * 8;
-                }
+        const int row = tid >> 2;
+        const int kp = tile * BN + row;
+        bool ok = kp >= lo_tile && kp <= pos_last;
+        const __nv_bfloat16* src = p.pages;
+        if (ok) {
+            const int block = kp / p.page_size;
+            const int page = block < p.max_blocks ? table[block] : -1;
+            if (page < 0 || page >= p.num_pages) {
+                if (p.error_flag) atomicExch(p.error_flag, 2);
+                ok = false;
+            } else {
+                src = p.pages + ((size_t)page * p.page_size + kp % p.page_size) * DK;
             }
-            cp_async16(&s.k[stage][row][piece * 8], src, ok);
         }
+#pragma unroll
+        for (int piece = tid & 3; piece < DK / 8; piece += 4)
+            cp_async16(&s.k[stage][row][piece * 8], ok ? src + piece * 8 : p.pages, ok);
     };
     if (t_begin < t_end) load_keys(0, t_begin);
     cp_async_commit();
@@ -149,14 +150,22 @@ latent_mma_kernel(Params p) {
         if (tile + 1 < t_end) load_keys(stage ^ 1, tile + 1);
         cp_async_commit();
         // ---- scores of this warp's 8 keys
-        float sc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-        for (int ks = 0; ks < DK / 16; ++ks) {
+        float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f};      // two chains: a product need not wait for the one before it
+#pragma unroll 2
+        for (int ks = 0; ks < DK / 16; ks += 2) {
             unsigned a[4], b[2];
             ldmatrix_x4(a, &s.q[a_row][ks * 16 + a_col]);
             ldmatrix_x2(b, &s.k[stage][warp * 8 + (lane & 7)][ks * 16 + 8 * ((lane >> 3) & 1)]);
             mma_bf16(sc, a, b[0], b[1]);
+            if (ks + 1 < DK / 16) {
+                unsigned a2[4], b2[2];
+                ldmatrix_x4(a2, &s.q[a_row][(ks + 1) * 16 + a_col]);
+                ldmatrix_x2(b2, &s.k[stage][warp * 8 + (lane & 7)][(ks + 1) * 16 + 8 * ((lane >> 3) & 1)]);
+                mma_bf16(sc2, a2, b2[0], b2[1]);
+            }
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[i] += sc2[i];
         const int key0 = tile * BN + warp * 8 + 2 * (lane & 3);
         float part_max[2];
 #pragma unroll

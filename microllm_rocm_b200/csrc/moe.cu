@@ -1,8 +1,8 @@
 // Routing of tokens to experts, on the device from start to end (nothing here needs the host to know a count):
 //
-//   moe_route     per token: z[e] = x . Wr[e] + b[e] in fp32; the `top` largest (ties: the smaller index) in order of
-//                 size; weights = softmax over those chosen logits only.  Optionally one more dot product with a
-//                 single row (the gate of a shared expert) whose sigmoid is stored per token.
+//   moe_select    per token, from router logits that a product left in fp32: z[e] = logits[e] + b[e]; the `top` largest
+//                 (ties: the smaller index) in order of size; weights = softmax over those chosen logits only.
+//                 Optionally one more column (the gate of a shared expert) whose sigmoid is stored per token.
 //   moe_align     from ids[T*top] to a list of the pairs (token, choice) sorted by expert: offsets[E+1] and
 //                 sorted[T*top] (pair indices); the order inside an expert is arbitrary, every pair's result is
 //                 computed on its own.
@@ -18,55 +18,57 @@ namespace {
 
 constexpr int ROUTE_WARPS = 4;
 constexpr int MAX_EXPERTS = 1024;
-constexpr int MAX_TOP = 32;
+constexpr int MAX_TOP = 32;       // one chosen logit per lane
 
-template <typename XT, typename WT>
+// logits [T, ld] fp32 (or `n_partials` partial sums of a split product, `partial_stride` elements apart): columns
+// 0..experts-1 are the router's, column `gate_col` (if >= 0) the pre-activation of a shared expert's gate.
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-moe_route_kernel(const XT* __restrict__ x, const WT* __restrict__ wr, const float* __restrict__ bias,
-                 const WT* __restrict__ shared_gate, int tokens, int width, int experts, int top,
-                 int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ gate_out) {
+moe_select_kernel(const float* __restrict__ logits, long long ld, int n_partials, long long partial_stride,
+                  const float* __restrict__ bias, int gate_col, int tokens, int experts, int top,
+                  int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ gate_out) {
     pdl_prologue();
     extern __shared__ float logits_s[];                 // [ROUTE_WARPS][experts]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * ROUTE_WARPS + warp;
     if (t >= tokens) return;
     float* z = logits_s + (size_t)warp * experts;
-    const XT* xr = x + (size_t)t * width;
-    for (int e = 0; e < experts; ++e) {
-        const WT* w = wr + (size_t)e * width;
-        float part = 0.0f;
-        for (int c = lane; c < width; c += 32) part = fmaf(to_f32(xr[c]), to_f32(w[c]), part);
-        part = warp_sum(part);
-        if (lane == 0) z[e] = part + (bias ? bias[e] : 0.0f);
+    const float* row = logits + (size_t)t * ld;
+    for (int e = lane; e < experts; e += 32) {
+        float v = row[e];
+        for (int k = 1; k < n_partials; ++k) v += row[(size_t)k * partial_stride + e];
+        z[e] = v + (bias ? bias[e] : 0.0f);
     }
-    if (shared_gate && gate_out) {
-        float part = 0.0f;
-        for (int c = lane; c < width; c += 32) part = fmaf(to_f32(xr[c]), to_f32(shared_gate[c]), part);
-        part = warp_sum(part);
-        if (lane == 0) gate_out[t] = 1.0f / (1.0f + expf(-part));
+    if (gate_col >= 0 && gate_out && lane == 0) {
+        float v = row[gate_col];
+        for (int k = 1; k < n_partials; ++k) v += row[(size_t)k * partial_stride + gate_col];
+        gate_out[t] = 1.0f / (1.0f + expf(-v));
     }
     __syncwarp();
-    if (lane == 0) {
-        float chosen[MAX_TOP];
-        unsigned taken[MAX_EXPERTS / 32];
-        for (int e = 0; e < (experts + 31) / 32; ++e) taken[e] = 0u;
-        for (int j = 0; j < top; ++j) {
-            int best = -1;
-            float best_v = -INFINITY;
-            for (int e = 0; e < experts; ++e) {
-                if ((taken[e >> 5] >> (e & 31)) & 1u) continue;
-                const float v = z[e];
-                if (best < 0 || v > best_v) { best = e; best_v = v; }
-            }
-            chosen[j] = best_v;
-            ids[(size_t)t * top + j] = best;
-            taken[best >> 5] |= 1u << (best & 31);
+    // `top` rounds of a warp-wide argmax (ties: the smaller index); a chosen logit is marked by its index in `taken`
+    float chosen = 0.0f, first = 0.0f, sum = 0.0f;      // lane j keeps the j-th chosen logit
+    for (int j = 0; j < top; ++j) {
+        float best_v = -INFINITY;
+        int best = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float v = z[e];
+            if (v != v) continue;                       // a logit that is not a number is never chosen before the others
+            if (best == 0x7fffffff || v > best_v) { best = e; best_v = v; }
         }
-        const float m = chosen[0];                      // the first choice is the largest
-        float sum = 0.0f;
-        for (int j = 0; j < top; ++j) { chosen[j] = expf(chosen[j] - m); sum += chosen[j]; }
-        for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] = chosen[j] / sum;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best, o);
+            if (oe != 0x7fffffff && (best == 0x7fffffff || ov > best_v || (ov == best_v && oe < best))) { best = oe; best_v = ov; }
+        }
+        if (best == 0x7fffffff) { best = 0; best_v = 0.0f; }      // nothing left that is a number
+        if (j == 0) first = best_v;
+        if (lane == (j & 31)) chosen = best_v;
+        if (lane == 0) { ids[(size_t)t * top + j] = best; z[best] = nanf(""); }
+        __syncwarp();
     }
+    const float w = lane < top ? expf(chosen - first) : 0.0f;
+    sum = warp_sum(w);
+    if (lane < top) weights[(size_t)t * top + lane] = w / sum;
 }
 
 __global__ void __launch_bounds__(1024)
@@ -114,22 +116,17 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
 
 }  // namespace
 
-MLB_EXPORT int mlb_moe_route(const void* x, const void* router, const float* bias, const void* shared_gate, int dtype, int tokens,
-                             int width, int experts, int top, int* ids, float* weights, float* gate_out, cudaStream_t stream) {
-    if (tokens < 0 || width <= 0 || experts <= 0 || experts > MAX_EXPERTS || top <= 0 || top > experts || top > MAX_TOP)
-        return fail(MLB_INVALID_ARGUMENT, "moe_route: bad sizes (experts %d, top %d; at most %d and %d)", experts, top, MAX_EXPERTS, MAX_TOP);
+MLB_EXPORT int mlb_moe_select(const float* logits, long long ld, int n_partials, long long partial_stride, const float* bias,
+                              int gate_col, int tokens, int experts, int top, int* ids, float* weights, float* gate_out,
+                              cudaStream_t stream) {
+    if (tokens < 0 || experts <= 0 || experts > MAX_EXPERTS || top <= 0 || top > experts || top > MAX_TOP || n_partials < 1 ||
+        ld < experts || gate_col >= ld)
+        return fail(MLB_INVALID_ARGUMENT, "moe_select: bad sizes (experts %d, top %d; at most %d and %d)", experts, top, MAX_EXPERTS, MAX_TOP);
     if (tokens == 0) return MLB_OK;
     const unsigned blocks = (tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
-    const size_t smem = (size_t)ROUTE_WARPS * experts * sizeof(float);
-    if (dtype == MLB_F32)
-        launch_kernel(moe_route_kernel<float, float>, blocks, ROUTE_WARPS * 32, smem, stream, (const float*)x, (const float*)router, bias,
-                      (const float*)shared_gate, tokens, width, experts, top, ids, weights, gate_out);
-    else if (dtype == MLB_BF16)
-        launch_kernel(moe_route_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, ROUTE_WARPS * 32, smem, stream, (const __nv_bfloat16*)x,
-                      (const __nv_bfloat16*)router, bias, (const __nv_bfloat16*)shared_gate, tokens, width, experts, top, ids, weights, gate_out);
-    else
-        return fail(MLB_INVALID_ARGUMENT, "moe_route: unknown dtype %d", dtype);
-    return check_launch("moe_route");
+    launch_kernel(moe_select_kernel, blocks, ROUTE_WARPS * 32, (size_t)ROUTE_WARPS * experts * sizeof(float), stream, logits, ld,
+                  n_partials, partial_stride, bias, gate_col, tokens, experts, top, ids, weights, gate_out);
+    return check_launch("moe_select");
 }
 
 MLB_EXPORT int mlb_moe_align(const int* ids, int pairs, int experts, int* offsets, int* sorted, int* error_flag, cudaStream_t stream) {

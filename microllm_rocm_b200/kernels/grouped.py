@@ -45,6 +45,15 @@ def mma_supported(a: torch.Tensor, weight: torch.Tensor, a_group_cols: int = 0) 
             and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
+def row_tile_for(rows: int, groups: int, listed: bool, tensor_cores: bool) -> int:
+    """Rows of a CTA's tile: 16 while a group holds few rows (decoding: a CTA should not multiply rows that do not
+    exist), 128 on the tensor cores once the groups are large (twice the reuse of every weight tile), else 64."""
+    per_group = rows / max(1, groups) if listed else rows
+    if per_group <= 16:
+        return 16
+    return 128 if tensor_cores and per_group >= 96 else 64
+
+
 def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, rows: int, a_group_cols: int = 0,
                    c_group_cols: int = 0, group_offsets: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None,
                    c_rows: Optional[torch.Tensor] = None, a_row_div: int = 1, factor: Optional[torch.Tensor] = None,
@@ -71,6 +80,8 @@ def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, 
         ops._need(factor, "factor", torch.float32, 2)
         if factor.shape[1] < out.shape[1]:
             raise KernelError("grouped_linear: the factor matrix is narrower than the output")
+    if row_tile == 128 and not mma_supported(a, weight, a_group_cols):
+        row_tile = 64
     if mma_supported(a, weight, a_group_cols):
         L = ops.lib(MMA_SOURCE)
         build.check(L, L.mlb_grouped_mma(
@@ -107,6 +118,7 @@ def grouped_silu_mul(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *
             group_offsets.data_ptr(), ops._ptr(a_rows), None, int(a_row_div), None, 0, F, int(rows), F, K, G,
             ops.dtype_tag(out), int(row_tile), ops._stream()))
         return
+    row_tile = min(row_tile, 64)
     gate_up = alloc((rows, two_f), a.dtype) if alloc is not None else torch.empty((rows, two_f), dtype=a.dtype, device=a.device)
     grouped_linear(a, weight, gate_up, rows=rows, group_offsets=group_offsets, a_rows=a_rows, a_row_div=a_row_div, row_tile=row_tile)
     ops.silu_mul(gate_up, out)

@@ -1,4 +1,4 @@
-"""Routing of tokens to experts on the device (`csrc/moe.cu`): router logits, choice and weights; the list of
+"""Routing of tokens to experts on the device (`csrc/moe.cu`): choice and weights from the router's logits; the list of
 (token, choice) pairs sorted by expert; the weighted sum of the experts' results."""
 from __future__ import annotations
 
@@ -12,8 +12,8 @@ from .build import KernelError
 
 SOURCE = "moe.cu"
 ops.register_signatures(SOURCE, {
-    "mlb_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                      c_void_p],
+    "mlb_moe_select": [c_void_p, c_longlong, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                       c_void_p],
     "mlb_moe_align": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "mlb_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                         c_void_p],
@@ -24,30 +24,34 @@ def sources():
     return [(SOURCE, {})]
 
 
-def route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor,
-          weights: torch.Tensor, shared_gate: Optional[torch.Tensor] = None, gate_out: Optional[torch.Tensor] = None) -> None:
-    """x [T, W] and router [E, W] in one dtype; bias [E] fp32.  ids [T, top] int32 and weights [T, top] fp32 receive the
-    chosen experts in order of their logits and the softmax over the chosen logits.  shared_gate [1, W] (x's dtype)
-    and gate_out [T] fp32: sigmoid(x . shared_gate) per token."""
-    ops._need(x, "x", dims=2); ops._need(router, "router", x.dtype, 2)
+def select(logits: torch.Tensor, experts: int, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor, weights: torch.Tensor,
+           gate_col: int = -1, gate_out: Optional[torch.Tensor] = None) -> None:
+    """logits [T, N] fp32 (or [S, T, N] partial sums of a split product), N >= experts: the router's logits in the first
+    `experts` columns, bias [experts] fp32 added here.  ids [T, top] int32 and weights [T, top] fp32 receive the chosen
+    experts in order of their logits and the softmax over the chosen logits.  gate_col >= 0 and gate_out [T] fp32:
+    sigmoid of that column per token."""
+    n_partials, stride, first = 1, 0, logits
+    if logits.dim() == 3:
+        ops._need(logits, "logits", torch.float32, 3)
+        n_partials, stride, first = logits.shape[0], logits.shape[1] * logits.shape[2], logits[0]
+    ops._need(first, "logits", torch.float32, 2)
     ops._need(ids, "ids", torch.int32, 2); ops._need(weights, "weights", torch.float32, 2)
-    T, W = x.shape
-    E = router.shape[0]
-    if router.shape[1] != W or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top):
-        raise KernelError("moe.route: shapes do not agree")
+    T, N = first.shape
+    if N < experts or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top) or gate_col >= N:
+        raise KernelError("moe.select: shapes do not agree")
     if bias is not None:
         ops._need(bias, "bias", torch.float32, 1)
-        if bias.shape[0] != E:
-            raise KernelError("moe.route: one bias per expert")
-    if (shared_gate is None) != (gate_out is None):
-        raise KernelError("moe.route: the shared gate's row and its output come together")
-    if shared_gate is not None:
-        ops._need(shared_gate, "shared_gate", x.dtype); ops._need(gate_out, "gate_out", torch.float32, 1)
-        if shared_gate.numel() != W or gate_out.shape[0] != T:
-            raise KernelError("moe.route: the shared gate is one row of the input's width, its output one number per token")
+        if bias.shape[0] != experts:
+            raise KernelError("moe.select: one bias per expert")
+    if (gate_col >= 0) != (gate_out is not None):
+        raise KernelError("moe.select: the gate's column and its output come together")
+    if gate_out is not None:
+        ops._need(gate_out, "gate_out", torch.float32, 1)
+        if gate_out.shape[0] != T:
+            raise KernelError("moe.select: one gate per token")
     L = ops.lib(SOURCE)
-    build.check(L, L.mlb_moe_route(x.data_ptr(), router.data_ptr(), ops._ptr(bias), ops._ptr(shared_gate), ops.dtype_tag(x),
-                                   T, W, E, int(top), ids.data_ptr(), weights.data_ptr(), ops._ptr(gate_out), ops._stream()))
+    build.check(L, L.mlb_moe_select(first.data_ptr(), first.stride(0), n_partials, stride, ops._ptr(bias), int(gate_col), T,
+                                    int(experts), int(top), ids.data_ptr(), weights.data_ptr(), ops._ptr(gate_out), ops._stream()))
 
 
 def align(ids: torch.Tensor, experts: int, offsets: torch.Tensor, sorted_pairs: torch.Tensor,

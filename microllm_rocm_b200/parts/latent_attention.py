@@ -135,7 +135,7 @@ class LatentAttention(Mixer):
                        inv_freq=self.inv_freq, rot_dims=self.rot_dims, q_plain=q_plain, q_full=q_full,
                        pages=cache.pages if cache.writable else None, gate_out=gate, heads=H, dim=self.dim,
                        rot_dim=self.rot_dim, rank=self.rank, error_flag=flag)
-        row_tile = 16 if T <= 16 else 64
+        row_tile = grouped.row_tile_for(T, H, False, grouped.mma_supported(q_plain, self.w_uk_t, self.dim))
         # a_h = Wuk_h^T q_h,plain into the first `rank` columns of each head's query row
         grouped.grouped_linear(q_plain, self.w_uk_t, q_full, rows=T, a_group_cols=self.dim, c_group_cols=self.kv_width,
                                row_tile=row_tile)

@@ -1,6 +1,6 @@
 """Routed experts: every token runs `top` of `experts` small gated feed-forwards and adds their results up.
 
-  z = Wr x + b                       fp32
+  z = Wr x + b                       fp32 (one product with the shared gate's row stacked under the router's)
   chosen = the `top` largest z;  w = softmax over the chosen z only
   y = sum_j w_j * down_e(silu(gate_e x) * up_e x)          e = chosen_j
   y += sigmoid(Wsg x) * shared(x)    a shared expert of the same form that every token runs (optional, its gate too)
@@ -16,7 +16,8 @@ from typing import Dict, Optional
 
 import torch
 
-from ..kernels import grouped, moe
+from ..kernels import gemm_bf16, grouped, moe
+from ..kernels.linear import linear
 from .base import FEED_FORWARDS, FeedForward, Runtime, StepContext, WeightSpec, make, register_feed_forward, scratch
 
 
@@ -46,7 +47,11 @@ class RoutedExperts(FeedForward):
             self.shared_prefix = shared.params.get("prefix", "")
             self.n_shared_gate = params.get("shared_gate_name")        # None: the shared expert is added ungated
         self.rt = rt
-        self.w_gate_up = self.w_down = self.w_router = self.b_router = self.w_shared_gate = None
+        # the router's rows and (behind them) the shared gate's row are ONE matrix on the device, its rows padded to a
+        # multiple of 8: one product gives every logit
+        self.has_gate = self.shared is not None and self.n_shared_gate is not None
+        self.router_rows = -(-(self.experts + (1 if self.has_gate else 0)) // 8) * 8
+        self.w_gate_up = self.w_down = self.w_router = self.b_router = None
 
     # --- declarations -----------------------------------------------------------------
     def weight_specs(self) -> Dict[str, WeightSpec]:
@@ -73,33 +78,39 @@ class RoutedExperts(FeedForward):
             g, u, d = (n.format(e) for n in self.expert_names)
             gate_up += [(g, e * 2 * ff), (u, e * 2 * ff + ff)]
             down.append((d, e * self.hidden))
+        router = [(self.n_router, 0)] + ([(self.n_shared_gate, E)] if self.has_gate else [])
         fused = {"experts.gate_up": (WeightSpec((E * 2 * ff, self.hidden)), gate_up),
-                 "experts.down": (WeightSpec((E * self.hidden, ff)), down)}
+                 "experts.down": (WeightSpec((E * self.hidden, ff)), down),
+                 "router.rows": (WeightSpec((self.router_rows, self.hidden)), router)}
         if self.shared is not None:
             for dest, (spec, pieces) in self.shared.fused_tensors().items():
                 fused[self.shared_prefix + dest] = (spec, [(self.shared_prefix + n, row) for n, row in pieces])
         return fused
 
     def kernel_sources(self):
-        own = grouped.sources() + moe.sources()
+        own = grouped.sources() + moe.sources() + ([] if self.rt.is_fp32 else gemm_bf16.sources(engine_only=True))
         return own + (self.shared.kernel_sources() if self.shared is not None else [])
 
     def bind(self, tensors):
         ff, E = self.inter, self.experts
         if "experts.gate_up" in tensors:
-            gate_up, down = tensors["experts.gate_up"], tensors["experts.down"]
+            gate_up, down, router = tensors["experts.gate_up"], tensors["experts.down"], tensors["router.rows"]
+            router[E + (1 if self.has_gate else 0):].zero_()             # the padding rows: their logits are never read
         else:                                  # the checkpoint's pieces: stack them
             names = [[n.format(e) for n in self.expert_names] for e in range(E)]
             gate_up = torch.cat([tensors[n] for g, u, _ in names for n in (g, u)], 0).contiguous()
             down = torch.cat([tensors[d] for _, _, d in names], 0).contiguous()
+            router = torch.zeros((self.router_rows, self.hidden), dtype=tensors[self.n_router].dtype, device=tensors[self.n_router].device)
+            router[:E] = tensors[self.n_router]
+            if self.has_gate:
+                router[E] = tensors[self.n_shared_gate].reshape(-1)
         self.w_gate_up = gate_up.view(E, 2 * ff, self.hidden)
         self.w_down = down.view(E, self.hidden, ff)
-        self.w_router = tensors[self.n_router]
+        self.w_router = router
         self.b_router = tensors[self.n_router_bias] if self.n_router_bias else None
         if self.shared is not None:
             n = len(self.shared_prefix)
             self.shared.bind({k[n:]: v for k, v in tensors.items() if k.startswith(self.shared_prefix)})
-            self.w_shared_gate = tensors[self.n_shared_gate] if self.n_shared_gate else None
 
     def replay_key(self):
         shared = None
@@ -107,11 +118,12 @@ class RoutedExperts(FeedForward):
             shared = self.shared.replay_key()
             if shared is None:
                 return None
-        return ("routed_experts", self.hidden, self.experts, self.top, self.inter, shared, self.n_shared_gate is not None,
-                self.b_router is not None)
+        if not self.rt.is_fp32 and not gemm_bf16._direct_library(self.rt.device):
+            return None                  # the library product would go through the tensor framework
+        return ("routed_experts", self.hidden, self.experts, self.top, self.inter, shared, self.has_gate, self.b_router is not None)
 
     def own_tensors(self):
-        own = [self.w_gate_up, self.w_down, self.w_router, self.b_router, self.w_shared_gate]
+        own = [self.w_gate_up, self.w_down, self.w_router, self.b_router]
         return own + (self.shared.own_tensors() if self.shared is not None else [])
 
     # --- compute ------------------------------------------------------------------------
@@ -122,13 +134,16 @@ class RoutedExperts(FeedForward):
         buf = lambda role, shape, dtype: scratch(ctx, "routed." + role, shape, dtype, dev)
         ids = buf("ids", (T, top), torch.int32)
         weights = buf("weights", (T, top), torch.float32)
-        gate = buf("shared_gate", (T,), torch.float32) if self.w_shared_gate is not None else None
-        moe.route(x, self.w_router, self.b_router, top, ids, weights, self.w_shared_gate, gate)
+        gate = buf("shared_gate", (T,), torch.float32) if self.has_gate else None
+        # every logit from one product (bf16 operands are multiplied exactly and summed in fp32; the fp32 path is fp32
+        # throughout); bias, choice, weights and the gate's sigmoid follow in fp32
+        logits = linear(x, self.w_router, None, torch.float32, partials_ok=True, error_flag=flag,
+                        alloc=lambda shape, dtype: buf("logits", shape, dtype))
+        moe.select(logits, E, self.b_router, top, ids, weights, E if self.has_gate else -1, gate)
         offsets = buf("offsets", (E + 1,), torch.int32)
         order = buf("order", (P,), torch.int32)
         moe.align(ids, E, offsets, order, flag)
-        # few rows per expert (decoding): narrow row tiles, so that a CTA does not multiply rows that do not exist
-        row_tile = 16 if P <= 16 * E else 64
+        row_tile = grouped.row_tile_for(P, E, True, grouped.mma_supported(x, self.w_gate_up))
         act = buf("act", (P, ff), self.rt.dtype)
         grouped.grouped_silu_mul(x, self.w_gate_up, act, rows=P, group_offsets=offsets, a_rows=order, a_row_div=top,
                                  row_tile=row_tile, alloc=lambda shape, dtype: buf("gate_up", shape, dtype))

@@ -80,6 +80,9 @@ def test_the_model_declares_the_checkpoints_names(key):
             last = layer["mlp"]["router"]["experts"] - 1
             assert pieces[f"l{i}.mlp.e{last}.up"] == (f"l{i}.mlp.experts.gate_up", last * 2 * ff + ff)
             assert pieces[f"l{i}.mlp.e{last}.down"] == (f"l{i}.mlp.experts.down", last * raw["width"])
+            assert pieces[f"l{i}.mlp.router"] == (f"l{i}.mlp.router.rows", 0)
+            if layer["mlp"].get("shared"):
+                assert pieces[f"l{i}.mlp.shared.sg"] == (f"l{i}.mlp.router.rows", last + 1)
     model.bind({n: t.float() for n, t in weights.items()})          # the pieces themselves bind too
     assert model.bound
 
