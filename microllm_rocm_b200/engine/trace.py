@@ -21,7 +21,7 @@ import sys
 from typing import List
 
 TRACE_PAGE_SIZE = 16       # divides the 64-token granularity in which --max-tokens is counted
-MAX_LIVE_REQUESTS = 8      # traces hold up to four at a time
+MAX_LIVE_REQUESTS = 4      # traces hold up to four at a time: slots are used again
 
 
 def parse_args(argv):
