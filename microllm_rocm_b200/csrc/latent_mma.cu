@@ -64,19 +64,23 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// STAGES key tiles are in shared memory or on their way: 2 for prompt portions (two CTAs share a multiprocessor), 4
+// for decoding, where a CTA owns few tiles and has all of them in flight at once.
+template <int STAGES>
 struct Smem {
     __nv_bfloat16 q[BM][KP];
-    __nv_bfloat16 k[2][BN][KP];
+    __nv_bfloat16 k[STAGES][BN][KP];
     __nv_bfloat16 p[BM][PP];
     float red_max[4][BM];
     float red_sum[4][BM];
 };
 
+template <int STAGES>
 __global__ void __launch_bounds__(128)
 latent_mma_kernel(Params p) {
     pdl_prologue();
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    Smem& s = *reinterpret_cast<Smem*>(smem_raw);
+    Smem<STAGES>& s = *reinterpret_cast<Smem<STAGES>*>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = p.work[2 * blockIdx.x], first_row = p.work[2 * blockIdx.x + 1];
     const int split = blockIdx.y;
@@ -120,8 +124,11 @@ latent_mma_kernel(Params p) {
         for (int piece = tid & 3; piece < DK / 8; piece += 4)
             cp_async16(&s.k[stage][row][piece * 8], ok ? src + piece * 8 : p.pages, ok);
     };
-    if (t_begin < t_end) load_keys(0, t_begin);
-    cp_async_commit();
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) {               // the first group holds Q as well
+        if (t_begin + i < t_end) load_keys(i, t_begin + i);
+        cp_async_commit();
+    }
 
     // this thread's two rows (lane / 4 and lane / 4 + 8): position and lower edge of each
     int row_pos[2], row_lo[2];
@@ -144,10 +151,10 @@ latent_mma_kernel(Params p) {
 
     const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
     for (int tile = t_begin; tile < t_end; ++tile) {
-        const int stage = (tile - t_begin) & 1;
-        cp_async_wait<0>();
-        __syncthreads();                                    // this tile's keys (and Q) have landed; the other stage is free
-        if (tile + 1 < t_end) load_keys(stage ^ 1, tile + 1);
+        const int stage = (tile - t_begin) % STAGES;
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();                                    // this tile's keys (and Q) have landed; the stage used last is free
+        if (tile + STAGES - 1 < t_end) load_keys((tile - t_begin + STAGES - 1) % STAGES, tile + STAGES - 1);
         cp_async_commit();
         // ---- scores of this warp's 8 keys
         float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f};      // two chains: a product need not wait for the one before it
@@ -250,27 +257,66 @@ latent_mma_kernel(Params p) {
     }
 }
 
-// out[g, :] = sum_s O_s e^(m_s - m) / (sum_s l_s e^(m_s - m) + e^(sink - m)),  m = max(m_s, sink); splits in order
-__global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ sink,
-                                    __nv_bfloat16* __restrict__ out, int splits, int total_rows, int heads) {
+// out[g, :] = sum_s O_s e^(m_s - m) / (sum_s l_s e^(m_s - m) + e^(sink - m)),  m = max(m_s, sink); splits in order.
+// One block per row; the splits' weights are worked out once, then every thread sums four columns.
+constexpr int MAX_SPLITS = 64;
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ sink,
+                    __nv_bfloat16* __restrict__ out, int splits, int total_rows, int heads) {
     pdl_prologue();
+    __shared__ float weight[MAX_SPLITS];
     const int g = blockIdx.x;
-    float m = sink ? sink[g % heads] : -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((size_t)s * total_rows + g) * 2]);
-    float l = sink ? expf(sink[g % heads] - m) : 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = part_ml[((size_t)s * total_rows + g) * 2];
-        if (ms != -INFINITY) l += part_ml[((size_t)s * total_rows + g) * 2 + 1] * expf(ms - m);
-    }
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    for (int c = threadIdx.x; c < R; c += blockDim.x) {
-        float o = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[((size_t)s * total_rows + g) * 2];
-            if (ms != -INFINITY) o += part_o[((size_t)s * total_rows + g) * R + c] * expf(ms - m);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float ms[MAX_SPLITS / 32], ls[MAX_SPLITS / 32];
+        float m = sink ? sink[g % heads] : -INFINITY;
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS / 32; ++i) {
+            const int sp = lane + 32 * i;
+            ms[i] = -INFINITY; ls[i] = 0.0f;
+            if (sp < splits) {
+                const float2 v = *reinterpret_cast<const float2*>(part_ml + ((size_t)sp * total_rows + g) * 2);
+                ms[i] = v.x; ls[i] = v.y;
+            }
+            m = fmaxf(m, ms[i]);
         }
-        out[(size_t)g * R + c] = __float2bfloat16_rn(o * inv);
+        m = warp_max(m);
+        float l = 0.0f;
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS / 32; ++i) {
+            ms[i] = ms[i] == -INFINITY ? 0.0f : expf(ms[i] - m);
+            l += ls[i] * ms[i];
+        }
+        l = warp_sum(l) + (sink ? expf(sink[g % heads] - m) : 0.0f);
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS / 32; ++i)
+            if (lane + 32 * i < splits) weight[lane + 32 * i] = ms[i] * inv;
     }
+    __syncthreads();
+    for (int c = threadIdx.x * 4; c < R; c += blockDim.x * 4) {
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp = 0; sp < splits; ++sp) {
+            const float4 v = *reinterpret_cast<const float4*>(part_o + ((size_t)sp * total_rows + g) * R + c);
+            const float w = weight[sp];
+            o.x = fmaf(v.x, w, o.x); o.y = fmaf(v.y, w, o.y); o.z = fmaf(v.z, w, o.z); o.w = fmaf(v.w, w, o.w);
+        }
+        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)g * R + c) = __floats2bfloat162_rn(o.x, o.y);
+        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)g * R + c + 2) = __floats2bfloat162_rn(o.z, o.w);
+    }
+}
+
+template <int STAGES>
+int launch_attention(const Params& p, int num_work, cudaStream_t stream) {
+    static bool configured[MAX_DEVICES] = {false};
+    const size_t smem = sizeof(Smem<STAGES>);
+    if (!configured[device_index()]) {
+        if (cudaFuncSetAttribute(latent_mma_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return fail(MLB_UNSUPPORTED_SIZE, "latent_attention_mma: %zu bytes of shared memory per CTA are not available", smem);
+        configured[device_index()] = true;
+    }
+    launch_kernel(latent_mma_kernel<STAGES>, dim3(num_work, p.splits), 128, smem, stream, p);
+    return check_launch("latent_attention_mma");
 }
 
 }  // namespace
@@ -285,21 +331,15 @@ MLB_EXPORT int mlb_latent_attention_mma(const void* q, const void* pages, void* 
                                         float* part_o, float* part_ml, int max_blocks, int num_pages, int page_size,
                                         int heads, int window, int splits, int total_rows, float scale, int* error_flag,
                                         cudaStream_t stream) {
-    if (num_work < 0 || heads <= 0 || splits < 1 || splits > 65535 || total_rows < 0 || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0)
+    if (num_work < 0 || heads <= 0 || splits < 1 || splits > MAX_SPLITS || total_rows < 0 || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0)
         return fail(MLB_INVALID_ARGUMENT, "latent_attention_mma: bad sizes");
     if (splits > 1 && (!part_o || !part_ml)) return fail(MLB_INVALID_ARGUMENT, "latent_attention_mma: split keys need a workspace");
     if (num_work == 0) return MLB_OK;
-    static bool configured[MAX_DEVICES] = {false};
-    const size_t smem = sizeof(Smem);
-    if (!configured[device_index()]) {
-        if (cudaFuncSetAttribute(latent_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return fail(MLB_UNSUPPORTED_SIZE, "latent_attention_mma: %zu bytes of shared memory per CTA are not available", smem);
-        configured[device_index()] = true;
-    }
     Params p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, sink, seq_starts, seq_pos0, block_table, work,
              part_o, part_ml, max_blocks, num_pages, page_size, heads, window, splits, total_rows, scale, error_flag};
-    launch_kernel(latent_mma_kernel, dim3(num_work, splits), 128, smem, stream, p);
-    int status = check_launch("latent_attention_mma");
+    // shared keys: few tiles per CTA, all of them in flight at once (if four stages fit this device's shared memory)
+    const bool deep = splits > 1 && sizeof(Smem<4>) <= 200 * 1024;
+    int status = deep ? launch_attention<4>(p, num_work, stream) : launch_attention<2>(p, num_work, stream);
     if (status != MLB_OK || splits == 1) return status;
     launch_kernel(latent_merge_kernel, total_rows, 128, 0, stream, (const float*)part_o, (const float*)part_ml, sink,
                   (__nv_bfloat16*)out, splits, total_rows, heads);
