@@ -53,6 +53,12 @@ CASES = {
           "layers": [_layer(2, 16, 16, 32, 32, 16, 5000.0, experts=8, top=3, ff=32, shared_ff=48),
                      _layer(2, 16, 16, 32, 32, 16, 5000.0, experts=8, top=3, ff=32, shared_ff=48)],
           "loop": {"start": 1, "stop": 2, "times": 1}},
+    # awkward sizes: nothing is a multiple of 8 but the width (every kernel that moves 16-byte pieces must step aside)
+    "e": {"architecture": "Gedalix", "vocab": 101, "width": 72, "max_positions": 260, "embedding": {"scale": 1.5},
+          "norm": {"eps": 1e-5}, "residual_mult": 0.7,
+          "layers": [_layer(3, 10, 6, 14, 18, 6, 777.0, experts=9, top=3, ff=20, shared_ff=28),
+                     _layer(3, 10, 6, 14, 18, 6, 777.0, experts=9, top=3, ff=20, shared_ff=28)],
+          "loop": {"start": 0, "stop": 2, "times": 2}},
 }
 
 

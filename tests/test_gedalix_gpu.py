@@ -225,7 +225,7 @@ def test_tensor_core_grouped_product_equals_the_plain_one(rows, row_tile):
 
 
 # ------------------------------------------------------------------------------------------- whole models, every cut
-LENGTHS = {"a": [1, 2, 17, 70, 133], "b": [3, 9, 40, 65, 150], "c": [31, 129], "d": [5, 64, 97]}
+LENGTHS = {"a": [1, 2, 17, 70, 133], "b": [3, 9, 40, 65, 150], "c": [31, 129], "d": [5, 64, 97], "e": [2, 33, 140]}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
