@@ -4,8 +4,8 @@
 //     C[c_row(r), g * c_group_cols + n] = epilogue( sum_k A[a_row(r), g * a_group_cols + k] * W[g][n, k] )
 //
 // A CTA owns a tile of BM rows (128 or 64, or 16 when groups hold few rows) of ONE group by 64 output columns, and walks K in
-// steps of 32 through a three-stage ring filled with cp.async (16-byte pieces: rows of A are gathered through the
-// row list on the way in).  Fragments come out of shared memory with ldmatrix; rows of the ring are padded to 80
+// steps of 64 through a three-stage ring filled with cp.async (16-byte pieces: rows of A are gathered through the
+// row list on the way in).  Fragments come out of shared memory with ldmatrix; rows of the ring are padded to 144
 // bytes, which keeps the eight rows of an ldmatrix phase in different banks.
 // Epilogues: none; times a factor read at the output's own place (fp32); or DUAL: the weight holds two row blocks
 // (gate rows, then `dual_rows` further down the up rows), both are multiplied in the same pass and the result is
@@ -20,7 +20,10 @@ MLB_DEFINE_LAST_ERROR()
 
 namespace {
 
-constexpr int BN = 64, BK = 32, STAGES = 3, PITCH = BK + 8;     // elements per padded row of the ring
+constexpr int BN = 64, STAGES = 3;
+// K elements per step: 64, but 32 for the 128-row tile with two weight blocks (its accumulators leave no registers for
+// the fragments of four 16-wide steps; measured 609 against 736 us for gate/up of 12,288 rows)
+__host__ __device__ constexpr int bk_of(int bm, bool dual) { return (bm == 128 && dual) ? 32 : 64; }
 constexpr int MAX_GROUPS = 1024;       // with a list of offsets (the offsets travel through shared memory)
 
 struct MmaParams {
@@ -52,20 +55,21 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
 }
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + expf(-g)); }
 
-__host__ __device__ constexpr int threads_of(int bm) { return 128; }
+__host__ __device__ constexpr int threads_of(int bm) { return bm == 128 ? 256 : 128; }
 constexpr size_t smem_of(int bm, bool dual) {
-    return (size_t)STAGES * (bm + (dual ? 2 : 1) * BN) * PITCH * sizeof(__nv_bfloat16) + (2 * bm + 4 + MAX_GROUPS + 1) * sizeof(int);
+    return (size_t)STAGES * (bm + (dual ? 2 : 1) * BN) * (bk_of(bm, dual) + 8) * sizeof(__nv_bfloat16) + (2 * bm + 4 + MAX_GROUPS + 1) * sizeof(int);
 }
 
 template <typename OutT, int BM, bool DUAL>
-__global__ void __launch_bounds__(threads_of(BM))
+__global__ void __launch_bounds__(threads_of(BM), BM == 128 ? 2 : 1)
 grouped_mma_kernel(MmaParams p) {
     constexpr int THREADS = threads_of(BM);
+    constexpr int BK = bk_of(BM, DUAL), PITCH = BK + 8, PIECES = BK / 8;    // padded row of the ring; 16-byte pieces per row
     constexpr int WARPS_M = BM >= 64 ? 4 : 1;        // BM 128 and 64: four warps under one another; BM 16: side by side
     constexpr int MT = BM / (16 * WARPS_M);          // 16-row tiles per warp: 2 (BM 128: a weight fragment serves both) or 1
-    constexpr int WARPS_N = 4 / WARPS_M;             // 1 or 4
-    constexpr int WN = BN / WARPS_N;                 // columns per warp: 64 or 16
-    constexpr int NT = WN / 8;                       // n-tiles per warp: 8 or 2
+    constexpr int WARPS_N = (THREADS / 32) / WARPS_M;   // 2 (BM 128: eight warps), 1 or 4
+    constexpr int WN = BN / WARPS_N;                 // columns per warp: 32, 64 or 16
+    constexpr int NT = WN / 8;                       // n-tiles per warp: 4, 8 or 2
     constexpr int NB = DUAL ? 2 : 1;
     pdl_prologue();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -119,23 +123,49 @@ grouped_mma_kernel(MmaParams p) {
     const int n0 = blockIdx.x * BN;
     const int k_tiles = (p.K + BK - 1) / BK;
 
+    // Which pieces this thread copies never changes from one K tile to the next: their global addresses (null: zeros)
+    // and their places in a stage are worked out once, a K tile only adds its offset.
+    constexpr int A_PER = (BM * PIECES + THREADS - 1) / THREADS, W_PER = (BN * PIECES + THREADS - 1) / THREADS;
+    const __nv_bfloat16* a_src[A_PER];
+    const __nv_bfloat16* w_src[NB][W_PER];
+    int a_dst[A_PER], w_dst[W_PER], a_k[A_PER], w_k[W_PER];
+#pragma unroll
+    for (int i = 0; i < A_PER; ++i) {
+        const int e = tid + i * THREADS;
+        const int row = (e / PIECES) % BM, piece = e % PIECES;
+        const int a = e < BM * PIECES ? src_row[row] : -1;
+        a_src[i] = a >= 0 ? A + (size_t)a * p.lda + piece * 8 : nullptr;
+        a_dst[i] = e < BM * PIECES ? row * PITCH + piece * 8 : -1;
+        a_k[i] = piece * 8;
+    }
+#pragma unroll
+    for (int i = 0; i < W_PER; ++i) {
+        const int e = tid + i * THREADS;
+        const int row = (e / PIECES) % BN, piece = e % PIECES;
+        const int n = n0 + row;
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+            w_src[b][i] = (e < BN * PIECES && n < p.N) ? W + ((size_t)n + (size_t)b * p.dual_rows) * p.ldw + piece * 8 : nullptr;
+        w_dst[i] = e < BN * PIECES ? row * PITCH + piece * 8 : -1;
+        w_k[i] = piece * 8;
+    }
     auto load_stage = [&](int stage, int kt) {
         const int k0 = kt * BK;
-        // A: BM rows x 4 pieces of 8 elements
-        for (int e = tid; e < BM * 4; e += THREADS) {
-            const int row = e >> 2, piece = e & 3, k = k0 + piece * 8;
-            const int a = src_row[row];
-            const bool ok = a >= 0 && k < p.K;
-            cp_async16(&As[stage][row][piece * 8], ok ? (const void*)(A + (size_t)a * p.lda + k) : (const void*)p.A, ok);
+        __nv_bfloat16* a_stage = &As[stage][0][0];
+#pragma unroll
+        for (int i = 0; i < A_PER; ++i) {
+            if (a_dst[i] < 0) continue;
+            const bool ok = a_src[i] != nullptr && k0 + a_k[i] < p.K;
+            cp_async16(a_stage + a_dst[i], ok ? (const void*)(a_src[i] + k0) : (const void*)p.A, ok);
         }
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
-            for (int e = tid; e < BN * 4; e += THREADS) {
-                const int row = e >> 2, piece = e & 3, k = k0 + piece * 8;
-                const int n = n0 + row;
-                const bool ok = n < p.N && k < p.K;
-                cp_async16(&Ws[stage][b][row][piece * 8],
-                           ok ? (const void*)(W + ((size_t)n + (size_t)b * p.dual_rows) * p.ldw + k) : (const void*)p.W, ok);
+            __nv_bfloat16* w_stage = &Ws[stage][b][0][0];
+#pragma unroll
+            for (int i = 0; i < W_PER; ++i) {
+                if (w_dst[i] < 0) continue;
+                const bool ok = w_src[b][i] != nullptr && k0 + w_k[i] < p.K;
+                cp_async16(w_stage + w_dst[i], ok ? (const void*)(w_src[b][i] + k0) : (const void*)p.W, ok);
             }
         }
     };
