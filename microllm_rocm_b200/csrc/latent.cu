@@ -47,6 +47,8 @@ __device__ __forceinline__ float proj_at(const PrepareParams& p, size_t row_base
     return v;
 }
 
+constexpr int SLICE = 1024;        // query and gate columns per block
+
 template <typename QT, typename KVT>
 __global__ void __launch_bounds__(256)
 latent_prepare_kernel(PrepareParams p) {
@@ -58,6 +60,38 @@ latent_prepare_kernel(PrepareParams p) {
     const int half = p.rot_dims / 2;
     const int Dk = p.rank + p.rot_dim;
 
+    // blockIdx.y == 0: the token's cache row; blockIdx.y >= 1: a slice of SLICE query and gate columns
+    if (blockIdx.y > 0) {
+        const int per_head = p.dim + p.rot_dim;
+        const int q_cols = p.heads * per_head;
+        const int lo = (blockIdx.y - 1) * SLICE, hi = min(lo + SLICE, q_cols + (p.gate_out ? p.gate_width : 0));
+        for (int e = lo + threadIdx.x; e < hi; e += blockDim.x) {
+            if (e >= q_cols) {                                   // the gate's sigmoid
+                const int c = e - q_cols;
+                const float z = proj_at(p, row, p.gate_col + c);
+                p.gate_out[(size_t)t * p.gate_width + c] = 1.0f / (1.0f + expf(-z));
+                continue;
+            }
+            // queries: plain parts to q_plain, rotated parts into the tail of each head's row of q_full
+            const int h = e / per_head, i = e % per_head;
+            const float v = proj_at(p, row, p.q_col + e);
+            if (i < p.dim) {
+                ((QT*)p.q_plain)[((size_t)t * p.heads + h) * p.dim + i] = from_f32<QT>(v);
+                continue;
+            }
+            const int r = i - p.dim;
+            float out = v;
+            if (r < p.rot_dims) {
+                const int pair = r < half ? r : r - half;
+                const float angle = (float)pos * p.inv_freq[pair];
+                const float cs = cosf(angle), sn = sinf(angle);
+                const float other = proj_at(p, row, p.q_col + (long long)h * per_head + p.dim + (r < half ? r + half : r - half));
+                out = r < half ? v * cs - other * sn : v * cs + other * sn;
+            }
+            ((QT*)p.q_full)[((size_t)t * p.heads + h) * Dk + p.rank + r] = from_f32<QT>(out);
+        }
+        return;
+    }
     // where this token's cache row lives
     KVT* cache_row = nullptr;
     if (p.pages) {
@@ -94,32 +128,6 @@ latent_prepare_kernel(PrepareParams p) {
                 }
                 cache_row[p.rank + i] = from_f32<KVT>(out);
             }
-        }
-    }
-    // queries: plain parts to q_plain, rotated parts into the tail of each head's row of q_full
-    const int per_head = p.dim + p.rot_dim;
-    for (int e = threadIdx.x; e < p.heads * per_head; e += blockDim.x) {
-        const int h = e / per_head, i = e % per_head;
-        const float v = proj_at(p, row, p.q_col + e);
-        if (i < p.dim) {
-            ((QT*)p.q_plain)[((size_t)t * p.heads + h) * p.dim + i] = from_f32<QT>(v);
-            continue;
-        }
-        const int r = i - p.dim;
-        float out = v;
-        if (r < p.rot_dims) {
-            const int pair = r < half ? r : r - half;
-            const float angle = (float)pos * p.inv_freq[pair];
-            const float cs = cosf(angle), sn = sinf(angle);
-            const float other = proj_at(p, row, p.q_col + (long long)h * per_head + p.dim + (r < half ? r + half : r - half));
-            out = r < half ? v * cs - other * sn : v * cs + other * sn;
-        }
-        ((QT*)p.q_full)[((size_t)t * p.heads + h) * Dk + p.rank + r] = from_f32<QT>(out);
-    }
-    if (p.gate_out) {
-        for (int c = threadIdx.x; c < p.gate_width; c += blockDim.x) {
-            const float z = proj_at(p, row, p.gate_col + c);
-            p.gate_out[(size_t)t * p.gate_width + c] = 1.0f / (1.0f + expf(-z));
         }
     }
 }
@@ -232,10 +240,12 @@ MLB_EXPORT int mlb_latent_prepare(const float* proj, long long ld, int n_partial
     PrepareParams p{proj, ld, n_partials, partial_stride, q_col, kv_col, gate_col, norm_weight, eps, positions, token_seq,
                     block_table, max_blocks, inv_freq, rot_dims, q_plain, q_full, pages, gate_out, num_pages, page_size,
                     tokens, heads, dim, rot_dim, rank, gate_width, error_flag};
+    const int columns = heads * (dim + rot_dim) + (gate_out ? gate_width : 0);
+    const dim3 grid(tokens, 1 + (columns + SLICE - 1) / SLICE);
     if (q_dtype == MLB_F32 && (kv_dtype == MLB_F32 || !pages))
-        launch_kernel(latent_prepare_kernel<float, float>, tokens, 256, 0, stream, p);
+        launch_kernel(latent_prepare_kernel<float, float>, grid, 256, 0, stream, p);
     else if (q_dtype == MLB_BF16 && (kv_dtype == MLB_BF16 || !pages))
-        launch_kernel(latent_prepare_kernel<__nv_bfloat16, __nv_bfloat16>, tokens, 256, 0, stream, p);
+        launch_kernel(latent_prepare_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 256, 0, stream, p);
     else
         return fail(MLB_INVALID_ARGUMENT, "latent_prepare: unsupported dtypes %d / %d", q_dtype, kv_dtype);
     return check_launch("latent_prepare");
