@@ -45,11 +45,14 @@ def swiglu_expert(h: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: t
 
 
 def sink_softmax_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
-                           sink: Optional[torch.Tensor]) -> torch.Tensor:
-    """q, k [H, T, dk], v [H, T, dv] of one sequence; position i sees j <= i; returns [T, H, dv]."""
+                           sink: Optional[torch.Tensor], window: Optional[int] = None) -> torch.Tensor:
+    """q, k [H, T, dk], v [H, T, dv] of one sequence; position i sees j <= i (with a window: the last `window` of
+    them, itself included); returns [T, H, dv]."""
     H, T, _ = q.shape
     s = torch.einsum("hid,hjd->hij", q, k) * scale
     mask = torch.ones(T, T, dtype=torch.bool).tril()
+    if window is not None:
+        mask &= ~torch.ones(T, T, dtype=torch.bool).tril(-int(window))
     s = s.masked_fill(~mask, -math.inf)
     if sink is not None:
         s = torch.cat([s, sink.to(F)[:, None, None].expand(H, T, 1)], dim=-1)
@@ -75,7 +78,7 @@ def latent_attention(h: torch.Tensor, positions: torch.Tensor, w: Dict[str, torc
     value = (c @ g("uv").T).view(T, H, vdim).transpose(0, 1)
     qq = torch.cat([q[..., :dim].transpose(0, 1), q_rot], dim=-1)
     kk = torch.cat([k_plain, k_rot[None].expand(H, T, rot_dim)], dim=-1)
-    o = sink_softmax_attention(qq, kk, value, mixer["scale"], w.get(prefix + "sink")).reshape(T, H * vdim)
+    o = sink_softmax_attention(qq, kk, value, mixer["scale"], w.get(prefix + "sink"), mixer.get("window")).reshape(T, H * vdim)
     if prefix + "g" in w:
         o = o * torch.sigmoid(h @ g("g").T)
     return o @ g("o").T

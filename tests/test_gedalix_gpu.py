@@ -307,6 +307,43 @@ def test_far_keys_page_borders_and_the_sink_decide_the_output(tmp_path_factory, 
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_mixer_with_a_window_of_keys(dtype):
+    """Latent attention takes a window as a parameter (no Gedalix configuration sets one): a model description with
+    windows of 40 and 33 keys on its two layers, built from the same parts.  The cache manager gives pages behind a
+    window back while the request lives; keys just inside and just outside the window, in prompt portions and in decoded
+    tokens, at page borders (pages of 8 and 16), against the plain implementation with the same window."""
+    import dataclasses
+
+    from microllm_rocm_b200.config import GedalixConfig, get_architecture
+    from microllm_rocm_b200.config.spec import PartSpec
+    from microllm_rocm_b200.engine.loading import make_engine, prepare_kernels
+    from microllm_rocm_b200.parts.base import Runtime
+    from microllm_rocm_b200.parts.build import build_model
+    from microllm_rocm_b200.weights.loader import target_dtype
+    raw = raw_config("d")
+    weights = random_weights(raw, seed=31, sharp=4.0)
+    windows = [40, 33]
+    spec = get_architecture("Gedalix").build_spec(GedalixConfig.from_dict(raw))
+    layers = [dataclasses.replace(layer, mixer=PartSpec(layer.mixer.kind, {**layer.mixer.params, "window": w}))
+              for layer, w in zip(spec.layers, windows)]
+    spec = dataclasses.replace(spec, layers=layers)
+    plain_raw = raw_config("d")
+    for layer, w in zip(plain_raw["layers"], windows):
+        layer["mixer"]["window"] = w
+    reqs = {"w0": random_tokens(150, raw["vocab"], 41), "w1": random_tokens(77, raw["vocab"], 42)}
+    rt = Runtime(torch.device(DEV), torch.float32 if dtype == "float32" else torch.bfloat16)
+    for page_size, steps in ((8, steps_prefill_then_decode(reqs, tail=60)), (16, steps_portions(reqs, sizes=(39, 2, 41, 1, 33, 7)))):
+        model = build_model(spec, rt)
+        prepare_kernels(model)
+        model.bind({n: weights[n].to(device=DEV, dtype=target_dtype(ws.role, rt)).contiguous() for n, ws in model.expected_tensors().items()})
+        engine = make_engine(model, page_size, 64, 4, max_step_tokens=160)
+        assert set(engine.cache.groups) == {"window40", "window33"}
+        got = collect(engine, steps)
+        compare(got, "d-window", plain_raw, weights, reqs, dtype)
+        assert engine.cache.pages_released_by_window > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_from_the_first_token(folders, dtype):
     """One token per step from position 0 on, over many pages."""
     folder, raw, weights = folders["d"]
