@@ -5,7 +5,9 @@
 // out [T*H, R] are plain row-major matrices with Dk = R + DR.  A CTA of four warps owns 16 consecutive query rows
 // of ONE sequence (a work item: sequence, first row among the sequence's new rows) and walks the keys those rows may
 // see in tiles of 32 at absolute multiples of 32, through a two-stage ring filled by cp.async straight from the pages.
-//   scores   each warp takes 8 of the tile's 32 keys: S[16 x 8] = Q[16 x Dk] K^T, Q and K by ldmatrix
+//   scores   warp w multiplies every fourth 16-wide step of the contraction (w, w + 4, ...) for all 32 keys, with its
+//            columns of Q held in registers as A fragments for the whole kernel; the four partial S[16 x 32] meet in
+//            shared memory, and from there on warp w owns keys 8 w .. 8 w + 7
 //   softmax  running maximum and sum per row in fp32; the warps meet in shared memory for the row's maximum and sum
 //   values   P[16 x 32] goes to shared memory as bf16; each warp owns a quarter of the R output columns and adds
 //            P V for them (V = the first R columns of the same cache rows, fetched with ldmatrix.trans)
@@ -51,10 +53,6 @@ __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
     const unsigned a = (unsigned)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
-__device__ __forceinline__ void ldmatrix_x2(unsigned (&r)[2], const void* p) {
-    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
-}
 __device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
     const unsigned a = (unsigned)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
@@ -66,11 +64,15 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
 
 // STAGES key tiles are in shared memory or on their way: 2 for prompt portions (two CTAs share a multiprocessor), 4
 // for decoding, where a CTA owns few tiles and has all of them in flight at once.
+constexpr int KS = DK / 16;               // 16-wide steps along the score's contraction
+constexpr int KW = (KS + 3) / 4;          // of which a warp takes every fourth: w, w + 4, ...
+constexpr int SP = BN + 4;                // pitch of a row of partial scores, in floats
+
 template <int STAGES>
 struct Smem {
-    __nv_bfloat16 q[BM][KP];
     __nv_bfloat16 k[STAGES][BN][KP];
     __nv_bfloat16 p[BM][PP];
+    float part[4][BM][SP];                // each warp's partial scores of the tile
     float red_max[4][BM];
     float red_sum[4][BM];
 };
@@ -98,11 +100,23 @@ latent_mma_kernel(Params p) {
     const int t_begin = tile_first + (int)((long long)tile_count_all * split / p.splits);
     const int t_end = tile_first + (int)((long long)tile_count_all * (split + 1) / p.splits);
 
-    // Q: the tile's rows, zeros behind the last one
-    for (int e = tid; e < BM * (DK / 8); e += 128) {
-        const int row = e / (DK / 8), piece = e % (DK / 8);
-        const bool ok = row < rows;
-        cp_async16(&s.q[row][piece * 8], ok ? (const void*)(p.q + (row_base + row) * DK + piece * 8) : (const void*)p.q, ok);
+    // Q never touches shared memory: warp w multiplies the 16-wide steps w, w + 4, ... of the contraction for ALL 32 keys
+    // of a tile, so it needs only those columns of Q, and keeps them as A fragments for the whole kernel
+    // (fragment registers: (row g, k 2t..), (row g + 8, k 2t..), (row g, k 2t + 8..), (row g + 8, k 2t + 8..); g = lane / 4, t = lane % 4)
+    unsigned qa[KW][4];
+    {
+        const int g = lane >> 2, t2 = 2 * (lane & 3);
+        const __nv_bfloat16* q0 = p.q + (row_base + g) * DK;
+        const __nv_bfloat16* q1 = p.q + (row_base + g + 8) * DK;
+#pragma unroll
+        for (int i = 0; i < KW; ++i) {
+            const int col = (warp + 4 * i) * 16 + t2;
+            const bool in = warp + 4 * i < KS;
+            qa[i][0] = in && g < rows ? *reinterpret_cast<const unsigned*>(q0 + col) : 0u;
+            qa[i][1] = in && g + 8 < rows ? *reinterpret_cast<const unsigned*>(q1 + col) : 0u;
+            qa[i][2] = in && g < rows ? *reinterpret_cast<const unsigned*>(q0 + col + 8) : 0u;
+            qa[i][3] = in && g + 8 < rows ? *reinterpret_cast<const unsigned*>(q1 + col + 8) : 0u;
+        }
     }
     // Four threads share a cache row: each looks the row's page up ONCE per tile and copies every fourth 16-byte piece.
     auto load_keys = [&](int stage, int tile) {
@@ -125,7 +139,7 @@ latent_mma_kernel(Params p) {
             cp_async16(&s.k[stage][row][piece * 8], ok ? src + piece * 8 : p.pages, ok);
     };
 #pragma unroll
-    for (int i = 0; i < STAGES - 1; ++i) {               // the first group holds Q as well
+    for (int i = 0; i < STAGES - 1; ++i) {
         if (t_begin + i < t_end) load_keys(i, t_begin + i);
         cp_async_commit();
     }
@@ -153,26 +167,46 @@ latent_mma_kernel(Params p) {
     for (int tile = t_begin; tile < t_end; ++tile) {
         const int stage = (tile - t_begin) % STAGES;
         cp_async_wait<STAGES - 2>();
-        __syncthreads();                                    // this tile's keys (and Q) have landed; the stage used last is free
+        __syncthreads();                                    // this tile's keys have landed; the stage used last is free
         if (tile + STAGES - 1 < t_end) load_keys((tile - t_begin + STAGES - 1) % STAGES, tile + STAGES - 1);
         cp_async_commit();
-        // ---- scores of this warp's 8 keys
-        float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f};      // two chains: a product need not wait for the one before it
-#pragma unroll 2
-        for (int ks = 0; ks < DK / 16; ks += 2) {
-            unsigned a[4], b[2];
-            ldmatrix_x4(a, &s.q[a_row][ks * 16 + a_col]);
-            ldmatrix_x2(b, &s.k[stage][warp * 8 + (lane & 7)][ks * 16 + 8 * ((lane >> 3) & 1)]);
-            mma_bf16(sc, a, b[0], b[1]);
-            if (ks + 1 < DK / 16) {
-                unsigned a2[4], b2[2];
-                ldmatrix_x4(a2, &s.q[a_row][(ks + 1) * 16 + a_col]);
-                ldmatrix_x2(b2, &s.k[stage][warp * 8 + (lane & 7)][(ks + 1) * 16 + 8 * ((lane >> 3) & 1)]);
-                mma_bf16(sc2, a2, b2[0], b2[1]);
+        // ---- partial scores of all 32 keys over this warp's steps of the contraction (four independent accumulators)
+        float sp[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sp[j][i] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < KW; ++i) {
+            const int ks = warp + 4 * i;
+            if (ks < KS) {                                  // the same for the whole warp
+                unsigned b0[4], b1[4];
+                ldmatrix_x4(b0, &s.k[stage][(lane & 7) + 8 * (lane >> 4)][ks * 16 + 8 * ((lane >> 3) & 1)]);
+                ldmatrix_x4(b1, &s.k[stage][16 + (lane & 7) + 8 * (lane >> 4)][ks * 16 + 8 * ((lane >> 3) & 1)]);
+                mma_bf16(sp[0], qa[i], b0[0], b0[1]);
+                mma_bf16(sp[1], qa[i], b0[2], b0[3]);
+                mma_bf16(sp[2], qa[i], b1[0], b1[1]);
+                mma_bf16(sp[3], qa[i], b1[2], b1[3]);
             }
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sc[i] += sc2[i];
+        for (int j = 0; j < 4; ++j) {
+            *reinterpret_cast<float2*>(&s.part[warp][lane >> 2][j * 8 + 2 * (lane & 3)]) = make_float2(sp[j][0], sp[j][1]);
+            *reinterpret_cast<float2*>(&s.part[warp][(lane >> 2) + 8][j * 8 + 2 * (lane & 3)]) = make_float2(sp[j][2], sp[j][3]);
+        }
+        __syncthreads();
+        // ---- from here on warp w owns keys 8 w .. 8 w + 7 of the tile: their scores are the four warps' partial sums, in order
+        float sc[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float2 v = *reinterpret_cast<const float2*>(&s.part[0][(lane >> 2) + 8 * h][warp * 8 + 2 * (lane & 3)]);
+#pragma unroll
+            for (int w2 = 1; w2 < 4; ++w2) {
+                const float2 u = *reinterpret_cast<const float2*>(&s.part[w2][(lane >> 2) + 8 * h][warp * 8 + 2 * (lane & 3)]);
+                v.x += u.x; v.y += u.y;
+            }
+            sc[2 * h] = v.x; sc[2 * h + 1] = v.y;
+        }
         const int key0 = tile * BN + warp * 8 + 2 * (lane & 3);
         float part_max[2];
 #pragma unroll
