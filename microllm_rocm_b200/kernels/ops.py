@@ -163,7 +163,7 @@ def all_sources():
         out += attention.mma_sources(d) + attention.tc_sources(d)
     from . import gemm_bf16, latent
     return (out + gemm_bf16.sources() + [("gemv_noalloc.cu", {})] + part_sources()
-            + latent.mma_sources(64, 32) + latent.mma_sources(512, 64))
+            + latent.mma_sources(256, 32) + latent.mma_sources(512, 64))      # the widths of the presets
 
 
 # ------------------------------------------------------------------------------ basic
