@@ -41,6 +41,9 @@ def page_shape(need, page_size: int):
     """What one page of a paged entry holds: keys and values of every kv head, or one row per token."""
     if isinstance(need, PagedRowsNeed):
         return (page_size, need.width)
+    value_dim = getattr(need, "value_dim", None)
+    if value_dim is not None and value_dim != need.head_dim:
+        return (need.num_kv_heads * page_size * (need.head_dim + value_dim),)      # keys of all kv heads, then values
     return (2, need.num_kv_heads, page_size, need.head_dim)
 
 

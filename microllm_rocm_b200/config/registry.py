@@ -24,6 +24,9 @@ class Architecture:
     model_types: Tuple[str, ...] = ()
     # named configurations (name -> config.json keys) that `preset()` and the command line's --random-config offer
     presets: Dict[str, Dict[str, Any]] = field(default_factory=dict, hash=False, compare=False)
+    # (parsed config.json, tensor name -> shape of the weight file) -> config.json completed with sizes that only
+    # the tensors' shapes give; None: the configuration file says everything
+    sizes_from_tensors: Any = field(default=None, hash=False, compare=False)
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -113,7 +116,20 @@ def load_config(folder_or_file: str):
     with open(path, "r", encoding="utf-8") as f:
         raw = json.load(f)
     arch = architecture_of(raw)
+    if arch.sizes_from_tensors is not None and os.path.isdir(folder_or_file):
+        raw = arch.sizes_from_tensors(raw, tensor_shapes(folder_or_file))
     return arch, arch.config_class.from_dict(raw)
+
+
+def tensor_shapes(folder_or_file: str) -> Dict[str, Tuple[int, ...]]:
+    """Tensor name -> shape from the headers of a model folder's weight files (nothing else is read); empty when
+    there are none."""
+    from ..weights.safetensors import open_model_files
+    try:
+        files = open_model_files(folder_or_file)
+    except (OSError, ValueError):
+        return {}
+    return {name: tuple(f.infos[name].shape) for f in files for name in f.names()}
 
 
 _loaded = False
@@ -123,4 +139,4 @@ def _ensure_builtin() -> None:
     global _loaded
     if not _loaded:
         _loaded = True
-        from ..models import gedalix, qwen2  # noqa: F401  (they register themselves)
+        from ..models import gedalix, matidra, qwen2  # noqa: F401  (they register themselves)

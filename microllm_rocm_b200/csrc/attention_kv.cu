@@ -1,0 +1,286 @@
+// Softmax attention whose keys and values may have different widths, with the steps that come between the
+// projections and the scores:
+//
+//   mlb_qk_prepare          per head: rms norm of q and k with a shared weight (optional), rotation of the first `rot_dims`
+//                           elements in interleaved pairs (2i, 2i + 1) by position * freq[i] with cos and sin times
+//                           `magnitude` (optional), q times 1 + coef * ln(floor((pos + 1) / every) + 1) (optional);
+//                           q goes out in the compute dtype, k and v into the pages.  v may be the projected k itself.
+//   mlb_paged_attention_kv  plain attention over those pages: one warp per (query token, query head), keys in tiles of
+//                           32 at absolute multiples of 32 with a running maximum and sum (the order of every addition
+//                           depends on the position alone, not on how the tokens were cut into steps), optional window,
+//                           optional output gate: o * sigmoid(gate) with the gate read from a projection's fp32 output.
+//
+// A page holds the keys of every kv head [NKV, page_size, DK] and behind them the values [NKV, page_size, DV].
+// Everything here is fp32 arithmetic; the inputs are fp32 columns of a projection's output (or K-split partial
+// results, summed in split order).
+#include "common.cuh"
+
+using namespace mlb;
+
+MLB_DEFINE_LAST_ERROR()
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int MAX_D = 256;
+constexpr int PER_LANE = MAX_D / 32;
+
+struct Columns {               // a block of columns of fp32 rows, possibly K-split partial results
+    const float* base; long long ld; int n_partials; long long partial_stride;
+    __device__ __forceinline__ float at(long long row, int col) const {
+        const float* p = base + row * ld + col;
+        float v = p[0];
+        for (int k = 1; k < n_partials; ++k) v += p[(size_t)k * partial_stride];
+        return v;
+    }
+};
+
+struct PrepareParams {
+    Columns q, k, v;           // q: H * DK columns from q_col, k: G * DK, v: G * DV (v may alias k's columns)
+    int q_col, k_col, v_col;
+    const float* q_norm; const float* k_norm; float eps;
+    const float* freq; int rot_dims; float magnitude;
+    float temp_coef; int temp_every;
+    const int* positions; const int* token_seq; const int* block_table;
+    int max_blocks, num_pages, page_size;
+    void* q_out;               // [T, H * DK]
+    void* pages;
+    int T, H, G, DK, DV;
+    int* error_flag;
+};
+
+template <typename OutT, typename KVT>
+__global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p) {
+    pdl_prologue();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int items = p.H + 2 * p.G;
+    const long long item = (long long)blockIdx.x * WARPS + warp;
+    if (item >= (long long)p.T * items) return;
+    const int t = (int)(item / items), which = (int)(item % items);
+    const int pos = p.positions[t];
+    // where the item goes
+    KVT* page_row = nullptr;
+    const bool is_q = which < p.H, is_k = !is_q && which < p.H + p.G;
+    const int head = is_q ? which : (is_k ? which - p.H : which - p.H - p.G);
+    const int D = (is_q || is_k) ? p.DK : p.DV;
+    if (!is_q) {
+        if (!p.pages) return;
+        const int seq = p.token_seq[t];
+        const int block = pos / p.page_size;
+        const int page = block < p.max_blocks ? p.block_table[(size_t)seq * p.max_blocks + block] : -1;
+        if (page < 0 || page >= p.num_pages) {
+            if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+            return;
+        }
+        const size_t page_stride = (size_t)p.G * p.page_size * (p.DK + p.DV);
+        const size_t within = is_k ? ((size_t)head * p.page_size + pos % p.page_size) * p.DK
+                                   : (size_t)p.G * p.page_size * p.DK + ((size_t)head * p.page_size + pos % p.page_size) * p.DV;
+        page_row = (KVT*)p.pages + (size_t)page * page_stride + within;
+    }
+    const Columns& src = is_q ? p.q : (is_k ? p.k : p.v);
+    const int col = (is_q ? p.q_col : (is_k ? p.k_col : p.v_col)) + head * D;
+    float x[PER_LANE];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int c = lane + 32 * i;
+        x[i] = c < D ? src.at(t, col + c) : 0.0f;
+        ss = fmaf(x[i], x[i], ss);
+    }
+    if (is_q || is_k) {
+        const float* w = is_q ? p.q_norm : p.k_norm;
+        if (w) {
+            const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)D + p.eps);
+#pragma unroll
+            for (int i = 0; i < PER_LANE; ++i) {
+                const int c = lane + 32 * i;
+                if (c < D) x[i] = x[i] * inv * w[c];
+            }
+        }
+        if (p.freq && p.rot_dims > 0) {
+#pragma unroll
+            for (int i = 0; i < PER_LANE; ++i) {
+                const int c = lane + 32 * i;
+                const float other = __shfl_xor_sync(0xffffffffu, x[i], 1);     // the pair's other element sits in the next lane
+                if (c < p.rot_dims) {
+                    const float angle = (float)pos * p.freq[c >> 1];
+                    const float cs = cosf(angle) * p.magnitude, sn = sinf(angle) * p.magnitude;
+                    x[i] = (c & 1) ? x[i] * cs + other * sn : x[i] * cs - other * sn;
+                }
+            }
+        }
+        if (is_q && p.temp_every > 0) {
+            const float temp = 1.0f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.0f);
+#pragma unroll
+            for (int i = 0; i < PER_LANE; ++i) x[i] *= temp;
+        }
+    }
+    if (is_q) {
+        OutT* out = (OutT*)p.q_out + ((size_t)t * p.H + head) * p.DK;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) { const int c = lane + 32 * i; if (c < D) out[c] = from_f32<OutT>(x[i]); }
+    } else {
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) { const int c = lane + 32 * i; if (c < D) page_row[c] = from_f32<KVT>(x[i]); }
+    }
+}
+
+struct AttnParams {
+    const void* q;           // [T, NH * DK]
+    const void* pages;
+    void* out;               // [T, NH * DV]
+    const int* positions; const int* token_seq; const int* block_table;
+    int max_blocks, num_pages, page_size;
+    int tokens, num_heads, num_kv_heads, dk, dv;
+    int window;              // 0: all earlier keys
+    float scale;
+    Columns gate; int gate_col;      // gate.base null: no gate
+    int* error_flag;
+};
+
+template <typename QT, typename KVT, typename OutT>
+__global__ void __launch_bounds__(WARPS * 32) paged_attention_kv_kernel(AttnParams p) {
+    pdl_prologue();
+    __shared__ float q_s[WARPS][MAX_D];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * WARPS + warp;
+    if (item >= (long long)p.tokens * p.num_heads) return;
+    const int t = (int)(item / p.num_heads), h = (int)(item % p.num_heads);
+    const int DK = p.dk, DV = p.dv;
+    const int kvh = h / (p.num_heads / p.num_kv_heads);
+    const int pos = p.positions[t];
+    const int seq = p.token_seq[t];
+    const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+
+    const QT* qrow = (const QT*)p.q + ((size_t)t * p.num_heads + h) * DK;
+    for (int c = lane; c < DK; c += 32) q_s[warp][c] = to_f32(qrow[c]);
+    __syncwarp();
+
+    float acc[PER_LANE];
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) acc[i] = 0.0f;
+    float m = -INFINITY, l = 0.0f;
+    const size_t page_stride = (size_t)p.num_kv_heads * p.page_size * (DK + DV);
+    const size_t v_base = (size_t)p.num_kv_heads * p.page_size * DK;
+    const int* table = p.block_table + (size_t)seq * p.max_blocks;
+
+    for (int base = (lo / 32) * 32; base <= pos; base += 32) {
+        const int kp = base + lane;
+        bool valid = kp >= lo && kp <= pos;
+        long long k_off = -1, v_off = -1;
+        if (valid) {
+            const int block = kp / p.page_size;
+            const int page = block < p.max_blocks ? table[block] : -1;
+            if (page < 0 || page >= p.num_pages) {
+                if (p.error_flag) atomicExch(p.error_flag, 2);
+                valid = false;
+            } else {
+                const size_t row = (size_t)kvh * p.page_size + kp % p.page_size;
+                k_off = (long long)((size_t)page * page_stride + row * DK);
+                v_off = (long long)((size_t)page * page_stride + v_base + row * DV);
+            }
+        }
+        float s = -INFINITY;
+        if (valid) {
+            const KVT* krow = (const KVT*)p.pages + k_off;
+            float dot = 0.0f;
+            for (int c = 0; c < DK; ++c) dot = fmaf(q_s[warp][c], to_f32(krow[c]), dot);
+            s = dot * p.scale;
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        if (m_new == -INFINITY) continue;
+        const float prob = valid ? expf(s - m_new) : 0.0f;
+        const float corr = (m == -INFINITY) ? 0.0f : expf(m - m_new);
+        l = l * corr + warp_sum(prob);
+        m = m_new;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) acc[i] *= corr;
+        const unsigned valid_mask = __ballot_sync(0xffffffffu, valid);
+        for (int j = 0; j < 32; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, prob, j);
+            const long long off_j = __shfl_sync(0xffffffffu, v_off, j);
+            if (!((valid_mask >> j) & 1u)) continue;
+            const KVT* vrow = (const KVT*)p.pages + off_j;
+#pragma unroll
+            for (int i = 0; i < PER_LANE; ++i) {
+                const int c = lane + 32 * i;
+                if (c < DV) acc[i] = fmaf(pj, to_f32(vrow[c]), acc[i]);
+            }
+        }
+    }
+    OutT* orow = (OutT*)p.out + ((size_t)t * p.num_heads + h) * DV;
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int c = lane + 32 * i;
+        if (c < DV) {
+            float o = acc[i] * inv;
+            if (p.gate.base) {
+                const float g = p.gate.at(t, p.gate_col + h * DV + c);
+                o *= g >= 0.0f ? 1.0f / (1.0f + expf(-g)) : expf(g) / (1.0f + expf(g));
+            }
+            orow[c] = from_f32<OutT>(o);
+        }
+    }
+}
+
+}  // namespace
+
+MLB_EXPORT int mlb_qk_prepare(const float* src, long long ld, int n_partials, long long partial_stride, int q_col, int k_col,
+                              int v_col, const float* kv_src, long long kv_ld, int kv_partials, long long kv_partial_stride,
+                              const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_dims,
+                              float magnitude, float temp_coef, int temp_every, const int* positions, const int* token_seq,
+                              const int* block_table, int max_blocks, int num_pages, int page_size, void* q_out, int q_dtype,
+                              void* pages, int kv_dtype, int T, int H, int G, int DK, int DV, int* error_flag,
+                              cudaStream_t stream) {
+    // `src` holds q (and k, v when kv_src is null); `kv_src`, when given, holds k and v (a projection that went through
+    // another kernel first: the raw values of "values are the projected keys" come from the same place as k)
+    if (T < 0 || H <= 0 || G <= 0 || H % G || DK <= 0 || DV <= 0 || DK > MAX_D || DV > MAX_D)
+        return fail(MLB_UNSUPPORTED_SIZE, "qk_prepare: heads %d/%d, widths %d/%d (at most %d)", H, G, DK, DV, MAX_D);
+    if (rot_dims < 0 || rot_dims % 2 || rot_dims > DK) return fail(MLB_INVALID_ARGUMENT, "qk_prepare: rot_dims %d of %d", rot_dims, DK);
+    if (pages && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !block_table))
+        return fail(MLB_INVALID_ARGUMENT, "qk_prepare: bad cache geometry");
+    if (T == 0) return MLB_OK;
+    PrepareParams p{};
+    p.q = Columns{src, ld, n_partials, partial_stride};
+    p.k = p.v = kv_src ? Columns{kv_src, kv_ld, kv_partials, kv_partial_stride} : p.q;
+    p.q_col = q_col; p.k_col = k_col; p.v_col = v_col;
+    p.q_norm = q_norm; p.k_norm = k_norm; p.eps = eps; p.freq = freq; p.rot_dims = rot_dims; p.magnitude = magnitude;
+    p.temp_coef = temp_coef; p.temp_every = temp_every; p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
+    p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.q_out = q_out; p.pages = pages;
+    p.T = T; p.H = H; p.G = G; p.DK = DK; p.DV = DV; p.error_flag = error_flag;
+    const long long items = (long long)T * (H + 2 * G);
+    const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
+    const int kvd = pages ? kv_dtype : q_dtype;
+    if (q_dtype == MLB_F32 && kvd == MLB_F32) launch_kernel(qk_prepare_kernel<float, float>, blocks, WARPS * 32, 0, stream, p);
+    else if (q_dtype == MLB_BF16 && kvd == MLB_BF16) launch_kernel(qk_prepare_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, WARPS * 32, 0, stream, p);
+    else if (q_dtype == MLB_F32 && kvd == MLB_BF16) launch_kernel(qk_prepare_kernel<float, __nv_bfloat16>, blocks, WARPS * 32, 0, stream, p);
+    else return fail(MLB_INVALID_ARGUMENT, "qk_prepare: unsupported dtypes %d/%d", q_dtype, kv_dtype);
+    return check_launch("qk_prepare");
+}
+
+MLB_EXPORT int mlb_paged_attention_kv(const void* q, int q_dtype, const void* pages, int kv_dtype, void* out, int out_dtype,
+                                      const int* positions, const int* token_seq, const int* block_table, int max_blocks,
+                                      int num_pages, int page_size, int tokens, int num_heads, int num_kv_heads, int dk, int dv,
+                                      int window, float scale, const float* gate, long long gate_ld, int gate_partials,
+                                      long long gate_partial_stride, int gate_col, int* error_flag, cudaStream_t stream) {
+    if (tokens < 0 || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
+        return fail(MLB_INVALID_ARGUMENT, "paged_attention_kv: bad head counts %d/%d", num_heads, num_kv_heads);
+    if (dk <= 0 || dk > MAX_D || dv <= 0 || dv > MAX_D)
+        return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_kv: widths %d/%d not in 1..%d", dk, dv, MAX_D);
+    if (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0)
+        return fail(MLB_INVALID_ARGUMENT, "paged_attention_kv: bad cache geometry");
+    if (tokens == 0) return MLB_OK;
+    AttnParams p{q, pages, out, positions, token_seq, block_table, max_blocks, num_pages, page_size, tokens, num_heads,
+                 num_kv_heads, dk, dv, window, scale, Columns{gate, gate_ld, gate_partials < 1 ? 1 : gate_partials, gate_partial_stride},
+                 gate_col, error_flag};
+    const long long items = (long long)tokens * num_heads;
+    const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
+    if (q_dtype == MLB_F32 && kv_dtype == MLB_F32 && out_dtype == MLB_F32)
+        launch_kernel(paged_attention_kv_kernel<float, float, float>, blocks, WARPS * 32, 0, stream, p);
+    else if (q_dtype == MLB_BF16 && kv_dtype == MLB_BF16 && out_dtype == MLB_BF16)
+        launch_kernel(paged_attention_kv_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, blocks, WARPS * 32, 0, stream, p);
+    else
+        return fail(MLB_INVALID_ARGUMENT, "paged_attention_kv: unsupported dtypes %d/%d/%d", q_dtype, kv_dtype, out_dtype);
+    return check_launch("paged_attention_kv");
+}

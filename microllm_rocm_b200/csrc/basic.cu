@@ -208,9 +208,15 @@ __device__ __forceinline__ float stable_sigmoid(float v) {
     return e / (1.0f + e);
 }
 
+// the gate's activation: 0 = silu, 1 = the tanh form of gelu, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float gate_activation(float g, int act) {
+    if (act == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g * stable_sigmoid(g);
+}
+
 template <typename InT, typename OutT>
 __global__ void silu_mul_kernel(const InT* __restrict__ gate, const InT* __restrict__ up, long long in_stride,
-                                int n_partials, long long partial_stride, OutT* __restrict__ out, int rows, int width) {
+                                int n_partials, long long partial_stride, OutT* __restrict__ out, int rows, int width, int act) {
     pdl_prologue();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)rows * width) return;
@@ -221,12 +227,12 @@ __global__ void silu_mul_kernel(const InT* __restrict__ gate, const InT* __restr
         g += to_f32(gate[(size_t)k * partial_stride + r * in_stride + c]);
         u += to_f32(up[(size_t)k * partial_stride + r * in_stride + c]);
     }
-    out[i] = from_f32<OutT>(g * stable_sigmoid(g) * u);
+    out[i] = from_f32<OutT>(gate_activation(g, act) * u);
 }
 
 // bf16 in, bf16 out, eight elements per thread (16-byte loads and stores)
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
-                                       long long in_stride, __nv_bfloat16* __restrict__ out, int rows, int width) {
+                                       long long in_stride, __nv_bfloat16* __restrict__ out, int rows, int width, int act) {
     pdl_prologue();
     const int vec_per_row = width / 8;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -241,7 +247,7 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate, c
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-        o2[k] = __floats2bfloat162_rn(g.x * stable_sigmoid(g.x) * u.x, g.y * stable_sigmoid(g.y) * u.y);
+        o2[k] = __floats2bfloat162_rn(gate_activation(g.x, act) * u.x, gate_activation(g.y, act) * u.y);
     }
     *reinterpret_cast<uint4*>(out + (size_t)r * width + c) = ov;
 }
@@ -249,26 +255,40 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate, c
 // gate and up are two column blocks of one [rows, in_stride] matrix (the fused gate/up
 // projection) or two separate matrices; `in_stride` is their row pitch in elements.  The input
 // may be `n_partials` partial results `partial_stride` elements apart.
-MLB_EXPORT int mlb_silu_mul(const void* gate, const void* up, long long in_stride, int in_dtype, int n_partials,
-                            long long partial_stride, void* out, int out_dtype, int rows, int width,
-                            cudaStream_t stream) {
+static int gated_act_mul(const void* gate, const void* up, long long in_stride, int in_dtype, int n_partials,
+                         long long partial_stride, void* out, int out_dtype, int rows, int width, int act,
+                         cudaStream_t stream) {
+    if (act != 0 && act != 1) return fail(MLB_INVALID_ARGUMENT, "gated activation: unknown activation %d", act);
     if (rows < 0 || width <= 0 || in_stride < width || n_partials < 1) return fail(MLB_INVALID_ARGUMENT, "silu_mul: bad sizes");
     if (rows == 0) return MLB_OK;
     const long long n = (long long)rows * width;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (in_dtype == MLB_F32 && out_dtype == MLB_F32)
-        launch_kernel(silu_mul_kernel<float, float>, blocks, 256, 0, stream, (const float*)gate, (const float*)up, in_stride, n_partials, partial_stride, (float*)out, rows, width);
+        launch_kernel(silu_mul_kernel<float, float>, blocks, 256, 0, stream, (const float*)gate, (const float*)up, in_stride, n_partials, partial_stride, (float*)out, rows, width, act);
     else if (in_dtype == MLB_BF16 && out_dtype == MLB_BF16 && n_partials == 1 && width % 8 == 0 && in_stride % 8 == 0 &&
              (uintptr_t)gate % 16 == 0 && (uintptr_t)up % 16 == 0 && (uintptr_t)out % 16 == 0)
         launch_kernel(silu_mul_bf16x8_kernel, (unsigned)((n / 8 + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)gate,
-                      (const __nv_bfloat16*)up, in_stride, (__nv_bfloat16*)out, rows, width);
+                      (const __nv_bfloat16*)up, in_stride, (__nv_bfloat16*)out, rows, width, act);
     else if (in_dtype == MLB_BF16 && out_dtype == MLB_BF16)
-        launch_kernel(silu_mul_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, in_stride, n_partials, partial_stride, (__nv_bfloat16*)out, rows, width);
+        launch_kernel(silu_mul_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, in_stride, n_partials, partial_stride, (__nv_bfloat16*)out, rows, width, act);
     else if (in_dtype == MLB_F32 && out_dtype == MLB_BF16)
-        launch_kernel(silu_mul_kernel<float, __nv_bfloat16>, blocks, 256, 0, stream, (const float*)gate, (const float*)up, in_stride, n_partials, partial_stride, (__nv_bfloat16*)out, rows, width);
+        launch_kernel(silu_mul_kernel<float, __nv_bfloat16>, blocks, 256, 0, stream, (const float*)gate, (const float*)up, in_stride, n_partials, partial_stride, (__nv_bfloat16*)out, rows, width, act);
     else
         return fail(MLB_INVALID_ARGUMENT, "silu_mul: unsupported dtype pair %d -> %d", in_dtype, out_dtype);
     return check_launch("silu_mul");
+}
+
+MLB_EXPORT int mlb_silu_mul(const void* gate, const void* up, long long in_stride, int in_dtype, int n_partials,
+                            long long partial_stride, void* out, int out_dtype, int rows, int width,
+                            cudaStream_t stream) {
+    return gated_act_mul(gate, up, in_stride, in_dtype, n_partials, partial_stride, out, out_dtype, rows, width, 0, stream);
+}
+
+// the same with the gate's activation chosen by `act` (see gate_activation)
+MLB_EXPORT int mlb_gated_act_mul(const void* gate, const void* up, long long in_stride, int in_dtype, int n_partials,
+                                 long long partial_stride, void* out, int out_dtype, int rows, int width, int act,
+                                 cudaStream_t stream) {
+    return gated_act_mul(gate, up, in_stride, in_dtype, n_partials, partial_stride, out, out_dtype, rows, width, act, stream);
 }
 
 // ------------------------------------------------------------------ fp32 -> bf16 cast

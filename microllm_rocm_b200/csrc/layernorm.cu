@@ -1,0 +1,109 @@
+// Layer norm with weight and bias, fp32:  y = (v - mean(v)) / sqrt(mean((v - mean)^2) + eps) * w + b.
+//
+//   mlb_layernorm             y[r] = LN(x[rows[r]] or x[r]), stored in the compute dtype (the final norm on selected rows)
+//   mlb_scale_add_layernorm   x[r] <- LN(alpha * x[r] + s1 * sum_k d1[k][r] + s2 * sum_k d2[k][r]) in place (the stream of a
+//                             block that normalises AFTER its sums), and a copy of the new x[r] in the compute dtype
+//                             for the products that read it next.  d1/d2 may be K-split partial results, added in
+//                             split order; d2 is optional (two mixers side by side whose results are weighted).
+//
+// One block of a fixed size per row, the row kept in shared memory between the passes (mean, then the squared
+// deviations: the two-pass form), reductions in a fixed tree: a row's result depends on the row alone.
+#include "common.cuh"
+
+using namespace mlb;
+
+MLB_DEFINE_LAST_ERROR()
+
+namespace {
+
+constexpr int LN_THREADS = 256;
+
+struct LnParams {
+    float* x;                 // [*, width] fp32 (written by scale_add)
+    const float* d1; int n1; long long stride1; float s1;
+    const float* d2; int n2; long long stride2; float s2;
+    float alpha;
+    const float* weight; const float* bias;
+    void* out;                // compute-dtype copy, may be null
+    const int* rows;          // plain norm: source row of each output row, may be null
+    int width; float eps;
+};
+
+template <typename OutT, bool ADD>
+__global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(LnParams p) {
+    pdl_prologue();
+    extern __shared__ float row_s[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x, W = p.width;
+    const size_t src = (!ADD && p.rows) ? (size_t)p.rows[r] : (size_t)r;
+    float* xr = p.x + src * W;
+    float sum = 0.0f;
+    for (int c = threadIdx.x; c < W; c += LN_THREADS) {
+        float v = xr[c];
+        if (ADD) {
+            v *= p.alpha;
+            float a = 0.0f;
+            for (int k = 0; k < p.n1; ++k) a += p.d1[(size_t)k * p.stride1 + src * W + c];
+            v = fmaf(p.s1, a, v);
+            if (p.d2) {
+                float b = 0.0f;
+                for (int k = 0; k < p.n2; ++k) b += p.d2[(size_t)k * p.stride2 + src * W + c];
+                v = fmaf(p.s2, b, v);
+            }
+        }
+        row_s[c] = v;
+        sum += v;
+    }
+    const float mean = block_sum(sum, scratch) / (float)W;
+    float sq = 0.0f;
+    for (int c = threadIdx.x; c < W; c += LN_THREADS) { const float d = row_s[c] - mean; sq = fmaf(d, d, sq); }
+    const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)W + p.eps);
+    OutT* yr = p.out ? (OutT*)p.out + (size_t)r * W : nullptr;
+    for (int c = threadIdx.x; c < W; c += LN_THREADS) {
+        const float y = (row_s[c] - mean) * inv * p.weight[c] + p.bias[c];
+        if (ADD) xr[c] = y;
+        if (yr) yr[c] = from_f32<OutT>(y);
+    }
+}
+
+int launch(const LnParams& p, int n, int out_dtype, bool add, cudaStream_t stream, const char* what) {
+    if (n < 0 || p.width <= 0) return fail(MLB_INVALID_ARGUMENT, "%s: bad sizes", what);
+    if ((size_t)p.width * sizeof(float) > 200 * 1024) return fail(MLB_UNSUPPORTED_SIZE, "%s: a row of %d floats does not fit shared memory", what, p.width);
+    if (n == 0) return MLB_OK;
+    const size_t smem = (size_t)p.width * sizeof(float);
+    auto go = [&](auto kernel) -> int {
+        if (smem > 48 * 1024) {
+            static bool raised[MAX_DEVICES][4] = {};
+            const int slot = (add ? 2 : 0) + (out_dtype == MLB_BF16 ? 1 : 0);
+            if (!raised[device_index()][slot]) {
+                if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+                    return fail(MLB_CUDA_ERROR, "%s: cannot raise the shared-memory limit", what);
+                raised[device_index()][slot] = true;
+            }
+        }
+        launch_kernel(kernel, (unsigned)n, LN_THREADS, smem, stream, p);
+        return check_launch(what);
+    };
+    if (add) return out_dtype == MLB_BF16 ? go(layernorm_kernel<__nv_bfloat16, true>) : go(layernorm_kernel<float, true>);
+    return out_dtype == MLB_BF16 ? go(layernorm_kernel<__nv_bfloat16, false>) : go(layernorm_kernel<float, false>);
+}
+
+}  // namespace
+
+MLB_EXPORT int mlb_layernorm(const float* x, const float* weight, const float* bias, void* out, int out_dtype, const int* rows,
+                             int n, int width, float eps, cudaStream_t stream) {
+    if (!x || !weight || !bias || !out) return fail(MLB_INVALID_ARGUMENT, "layernorm: null operand");
+    LnParams p{};
+    p.x = const_cast<float*>(x); p.weight = weight; p.bias = bias; p.out = out; p.rows = rows; p.width = width; p.eps = eps;
+    return launch(p, n, out_dtype, false, stream, "layernorm");
+}
+
+MLB_EXPORT int mlb_scale_add_layernorm(float* x, float alpha, const float* d1, int n1, long long stride1, float s1, const float* d2,
+                                       int n2, long long stride2, float s2, const float* weight, const float* bias, void* out,
+                                       int out_dtype, int n, int width, float eps, cudaStream_t stream) {
+    if (!x || !d1 || !weight || !bias || n1 < 1 || (d2 && n2 < 1)) return fail(MLB_INVALID_ARGUMENT, "scale_add_layernorm: bad operands");
+    LnParams p{};
+    p.x = x; p.d1 = d1; p.n1 = n1; p.stride1 = stride1; p.s1 = s1; p.d2 = d2; p.n2 = n2; p.stride2 = stride2; p.s2 = s2;
+    p.alpha = alpha; p.weight = weight; p.bias = bias; p.out = out; p.width = width; p.eps = eps;
+    return launch(p, n, out_dtype, true, stream, "scale_add_layernorm");
+}

@@ -1,0 +1,124 @@
+// Short causal convolution over time, per channel, with the last taps - 1 inputs of every sequence kept as state:
+//
+//   y[t, c] = act( sum_j w[c, j] * u[t - taps + 1 + j, c] ),   u = 0 before the sequence's start, act = identity | silu
+//
+// u is a block of columns of a projection's fp32 output (or of its K-split partial results, added in split
+// order).  Tokens of a step are the flat batch of the engine: a sequence's tokens are consecutive, it held `pos0`
+// tokens before the step; inputs of positions before the step come from the state of the sequence's slot
+// ([slots, taps - 1, C] fp32, oldest first), inputs of positions before 0 are zero whatever the slot holds (a slot
+// is never cleared when a new request takes it).  `mlb_short_conv_state` then moves the state on; it runs after the
+// convolution has read the old one.
+#include "common.cuh"
+
+using namespace mlb;
+
+MLB_DEFINE_LAST_ERROR()
+
+namespace {
+
+constexpr int MAX_TAPS = 16;
+
+struct ConvParams {
+    const float* u; long long ld; int n_partials; long long partial_stride; int col0;
+    const float* w;            // [C, taps]
+    float* state;              // [slots + 1, taps - 1, C]
+    const int* slots;          // [A]
+    int num_slots;
+    const int* seq_starts;     // [A + 1]
+    const int* seq_pos0;       // [A]
+    const int* token_seq;      // [T]
+    float* y; long long ldy;
+    int T, A, C, taps, act;
+    int* error_flag;
+};
+
+__device__ __forceinline__ float input_at(const ConvParams& p, long long row, int c) {
+    const float* at = p.u + row * p.ld + p.col0 + c;
+    float v = at[0];
+    for (int k = 1; k < p.n_partials; ++k) v += at[(size_t)k * p.partial_stride];
+    return v;
+}
+
+__global__ void short_conv_kernel(ConvParams p) {
+    pdl_prologue();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)p.T * p.C) return;
+    const int t = (int)(i / p.C), c = (int)(i % p.C);
+    const int a = p.token_seq[t];
+    const int start = p.seq_starts[a], pos0 = p.seq_pos0[a];
+    const int local = t - start;
+    const int slot = p.slots[a];
+    const bool slot_ok = slot >= 0 && slot < p.num_slots;
+    if (!slot_ok && p.error_flag) atomicExch(p.error_flag, 3);
+    const int hist = p.taps - 1;
+    float acc = 0.0f;
+    for (int j = 0; j < p.taps; ++j) {
+        const int src = local - hist + j;              // index among this step's tokens of the sequence
+        float u = 0.0f;
+        if (src >= 0) u = input_at(p, (long long)start + src, c);
+        else if (pos0 + src >= 0 && slot_ok) u = p.state[((size_t)slot * hist + (hist + src)) * p.C + c];
+        acc = fmaf(p.w[(size_t)c * p.taps + j], u, acc);
+    }
+    if (p.act == 1) acc = acc / (1.0f + expf(-acc));
+    p.y[(size_t)t * p.ldy + c] = acc;
+}
+
+__global__ void short_conv_state_kernel(ConvParams p) {
+    pdl_prologue();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)p.A * p.C) return;
+    const int a = (int)(i / p.C), c = (int)(i % p.C);
+    const int start = p.seq_starts[a], n = p.seq_starts[a + 1] - start;
+    const int slot = p.slots[a];
+    if (slot < 0 || slot >= p.num_slots) return;
+    const int hist = p.taps - 1;
+    float keep[MAX_TAPS];
+    float* st = p.state + (size_t)slot * hist * p.C + c;
+#pragma unroll
+    for (int m = 0; m < MAX_TAPS; ++m) {
+        if (m >= hist) break;
+        const int src = n - hist + m;
+        keep[m] = src >= 0 ? input_at(p, (long long)start + src, c) : st[(size_t)(m + n) * p.C];
+    }
+#pragma unroll
+    for (int m = 0; m < MAX_TAPS; ++m) {
+        if (m >= hist) break;
+        st[(size_t)m * p.C] = keep[m];
+    }
+}
+
+int check(const ConvParams& p, const char* what) {
+    if (p.T < 0 || p.A < 0 || p.C <= 0 || p.taps < 1 || p.taps > MAX_TAPS + 1 || p.n_partials < 1 || p.num_slots <= 0)
+        return fail(MLB_INVALID_ARGUMENT, "%s: bad sizes (taps 1..%d)", what, MAX_TAPS + 1);
+    if (!p.u || !p.w || !p.slots || !p.seq_starts || !p.seq_pos0 || !p.token_seq || (p.taps > 1 && !p.state))
+        return fail(MLB_INVALID_ARGUMENT, "%s: null operand", what);
+    return MLB_OK;
+}
+
+}  // namespace
+
+MLB_EXPORT int mlb_short_conv(const float* u, long long ld, int n_partials, long long partial_stride, int col0, const float* w,
+                              float* state, const int* slots, int num_slots, const int* seq_starts, const int* seq_pos0,
+                              const int* token_seq, float* y, long long ldy, int T, int A, int C, int taps, int act,
+                              int* error_flag, cudaStream_t stream) {
+    ConvParams p{u, ld, n_partials, partial_stride, col0, w, state, slots, num_slots, seq_starts, seq_pos0, token_seq, y, ldy,
+                 T, A, C, taps, act, error_flag};
+    if (int s = check(p, "short_conv")) return s;
+    if (!y) return fail(MLB_INVALID_ARGUMENT, "short_conv: null output");
+    if (T == 0) return MLB_OK;
+    const long long n = (long long)T * C;
+    launch_kernel(short_conv_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, p);
+    return check_launch("short_conv");
+}
+
+MLB_EXPORT int mlb_short_conv_state(const float* u, long long ld, int n_partials, long long partial_stride, int col0, float* state,
+                                    const int* slots, int num_slots, const int* seq_starts, int A, int C, int taps,
+                                    cudaStream_t stream) {
+    ConvParams p{u, ld, n_partials, partial_stride, col0, u, state, slots, num_slots, seq_starts, seq_starts, seq_starts, nullptr, 0,
+                 0, A, C, taps, 0, nullptr};
+    if (int s = check(p, "short_conv_state")) return s;
+    if (A == 0 || taps == 1) return MLB_OK;
+    const long long n = (long long)A * C;
+    launch_kernel(short_conv_state_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, p);
+    return check_launch("short_conv_state");
+}

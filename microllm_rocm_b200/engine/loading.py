@@ -79,6 +79,9 @@ def load_engine(folder: str, dtype="bfloat16", page_size: int = DEFAULT_PAGE_SIZ
     with open(config_path or os.path.join(folder, "config.json"), "r", encoding="utf-8") as f:
         raw = json.load(f)
     arch = architecture_of(raw)
+    if arch.sizes_from_tensors is not None:          # sizes that only the tensors' shapes give
+        from ..config.registry import tensor_shapes
+        raw = arch.sizes_from_tensors(raw, tensor_shapes(weights_path or folder))
     config = arch.config_class.from_dict(raw)
     rt = Runtime(dev, resolve_dtype(dtype))
     model = build_model(arch.build_spec(config), rt)

@@ -1,0 +1,106 @@
+"""Softmax attention whose keys and values may differ in width (`csrc/attention_kv.cu`): the step between the
+projections and the scores (per-head rms norm, rotation of interleaved pairs, query temperature, cache store), and the
+attention itself with an optional sigmoid gate on its output.
+
+Pages hold the keys of all kv heads and then the values: [NKV, page, DK] + [NKV, page, DV] elements, which for equal
+widths is the layout [2, NKV, page, D] of the other attention kernels, so a mixer with DK == DV may prepare here and
+attend there.
+"""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build, ops
+from .build import KernelError
+
+MAX_WIDTH = 256
+
+ops.register_signatures("attention_kv.cu", {
+    "mlb_qk_prepare": [c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_longlong,
+                       c_void_p, c_void_p, c_float, c_void_p, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p,
+                       c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "mlb_paged_attention_kv": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_longlong, c_int, c_longlong, c_int,
+                               c_void_p, c_void_p],
+})
+
+
+def sources():
+    return [("attention_kv.cu", {})]
+
+
+def check_widths(dk: int, dv: int) -> None:
+    if not (0 < dk <= MAX_WIDTH and 0 < dv <= MAX_WIDTH):
+        raise KernelError(f"key width {dk} / value width {dv}: both must be in 1..{MAX_WIDTH}")
+
+
+def _columns(t: torch.Tensor, name: str):
+    """(first plane, row pitch, planes, plane stride) of fp32 rows or their [S, T, N] partial results."""
+    ops._need(t, name, torch.float32)
+    if t.dim() == 3:
+        return t, t.shape[2], t.shape[0], t.shape[1] * t.shape[2]
+    if t.dim() != 2:
+        raise KernelError(f"{name} must be [T, N] or [S, T, N]")
+    return t, t.shape[1], 1, 0
+
+
+def page_elements(num_kv_heads: int, page_size: int, dk: int, dv: int) -> int:
+    return num_kv_heads * page_size * (dk + dv)
+
+
+def qk_prepare(src: torch.Tensor, q_col: int, k_col: int, v_col: int, *, kv_src: Optional[torch.Tensor] = None,
+               q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float, freq: Optional[torch.Tensor],
+               rot_dims: int, magnitude: float, q_temp, positions: torch.Tensor, token_seq: torch.Tensor,
+               block_table: Optional[torch.Tensor], pages: Optional[torch.Tensor], page_size: int, q_out: torch.Tensor,
+               heads: int, kv_heads: int, dk: int, dv: int, error_flag: Optional[torch.Tensor]) -> None:
+    """q, k, v are column blocks (first columns q_col, k_col, v_col) of `src`; k and v of `kv_src` when that is given.
+    `q_temp`: None or (coef, every).  `pages` None: only the queries are made."""
+    _, ld, n, stride = _columns(src, "src")
+    kv_ptr, kv_ld, kv_n, kv_stride = None, 0, 0, 0
+    if kv_src is not None:
+        _, kv_ld, kv_n, kv_stride = _columns(kv_src, "kv_src")
+        kv_ptr = kv_src.data_ptr()
+    T = src.shape[-2]
+    ops._need(q_out, "q_out", dims=2)
+    if q_out.shape != (T, heads * dk):
+        raise KernelError("qk_prepare: q_out must be [T, heads * dk]")
+    num_pages = max_blocks = 0
+    if pages is not None:
+        ops._need(block_table, "block_table", torch.int32, 2)
+        if pages.numel() % pages.shape[0] or pages.numel() // pages.shape[0] != page_elements(kv_heads, page_size, dk, dv):
+            raise KernelError(f"qk_prepare: pages {tuple(pages.shape)} do not match the head geometry")
+        num_pages, max_blocks = pages.shape[0], block_table.shape[1]
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+    L = ops.lib("attention_kv.cu")
+    build.check(L, L.mlb_qk_prepare(
+        src.data_ptr(), ld, n, stride, q_col, k_col, v_col, kv_ptr, kv_ld, kv_n, kv_stride, ops._ptr(q_norm), ops._ptr(k_norm),
+        float(eps), ops._ptr(freq) if rot_dims else None, int(rot_dims), float(magnitude), coef, every, positions.data_ptr(),
+        token_seq.data_ptr(), ops._ptr(block_table), max_blocks, num_pages, page_size, q_out.data_ptr(), ops.dtype_tag(q_out),
+        ops._ptr(pages), ops.dtype_tag(pages) if pages is not None else ops.F32, T, heads, kv_heads, dk, dv,
+        ops._ptr(error_flag), ops._stream()))
+
+
+def paged_attention_kv(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
+                       block_table: torch.Tensor, page_size: int, heads: int, kv_heads: int, dk: int, dv: int, scale: float,
+                       window: Optional[int], gate: Optional[torch.Tensor], gate_col: int,
+                       error_flag: Optional[torch.Tensor]) -> None:
+    """out[T, heads * dv] = softmax(q k^T * scale) v (* sigmoid(gate columns gate_col.. of fp32 rows or partial results))."""
+    ops._need(q, "q", dims=2); ops._need(out, "out", dims=2); ops._need(block_table, "block_table", torch.int32, 2)
+    T = q.shape[0]
+    if q.shape[1] != heads * dk or out.shape != (T, heads * dv):
+        raise KernelError("paged_attention_kv: shapes do not agree")
+    if pages.numel() // pages.shape[0] != page_elements(kv_heads, page_size, dk, dv):
+        raise KernelError(f"paged_attention_kv: pages {tuple(pages.shape)} do not match the head geometry")
+    g_ptr, g_ld, g_n, g_stride = None, 0, 1, 0
+    if gate is not None:
+        _, g_ld, g_n, g_stride = _columns(gate, "gate")
+        g_ptr = gate.data_ptr()
+    L = ops.lib("attention_kv.cu")
+    build.check(L, L.mlb_paged_attention_kv(
+        q.data_ptr(), ops.dtype_tag(q), pages.data_ptr(), ops.dtype_tag(pages), out.data_ptr(), ops.dtype_tag(out),
+        positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], pages.shape[0], page_size, T,
+        heads, kv_heads, dk, dv, int(window or 0), float(scale), g_ptr, g_ld, g_n, g_stride, int(gate_col),
+        ops._ptr(error_flag), ops._stream()))

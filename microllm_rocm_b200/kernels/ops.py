@@ -63,6 +63,7 @@ _SIGNATURES = {
         "mlb_stream_join": [c_void_p, c_void_p],
         "mlb_add_inplace": [c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p],
         "mlb_silu_mul": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mlb_gated_act_mul": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mlb_cast_f32_bf16": [c_void_p, c_void_p, c_longlong, c_void_p],
         "mlb_copy_async": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
         "mlb_stream_synchronize": [c_void_p],
@@ -90,6 +91,11 @@ _SIGNATURES = {
                                    c_float, c_void_p],
         "mlb_add_scaled_inplace": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p],
         "mlb_stream_entry": [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p],
+    },
+    "layernorm.cu": {
+        "mlb_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
+        "mlb_scale_add_layernorm": [c_void_p, c_float, c_void_p, c_int, c_longlong, c_float, c_void_p, c_int, c_longlong, c_float,
+                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     },
     "sampling.cu": {
         "mlb_argmax_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
@@ -151,7 +157,8 @@ def base_sources():
 def part_sources():
     """(source, defines) of the kernels that only some kinds of parts ask for (each part names its own in
     `kernel_sources`)."""
-    return [("residual.cu", {}), ("grouped_gemm.cu", {}), ("grouped_mma.cu", {}), ("latent.cu", {}), ("moe.cu", {})]
+    return [("residual.cu", {}), ("grouped_gemm.cu", {}), ("grouped_mma.cu", {}), ("latent.cu", {}), ("moe.cu", {}),
+            ("layernorm.cu", {}), ("short_conv.cu", {}), ("attention_kv.cu", {}), ("delta_rule.cu", {})]
 
 
 def all_sources():
@@ -247,6 +254,33 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
                                   width, _stream()))
 
 
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out[r, c] = act(gate_up[r, c]) * gate_up[r, width + c], act = "silu" or "gelu_tanh" (the tanh form of gelu);
+    the input may be [S, rows, 2*width] partial results (summed over S in order first)."""
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gated_act_mul: unknown activation {activation!r}; known: {', '.join(ACTIVATIONS)}")
+    _need(out, "out", dims=2)
+    rows, width = out.shape
+    n_partials, partial_stride = 1, 0
+    if gate_up.dim() == 3:
+        _need(gate_up, "gate_up", dims=3)
+        n_partials, partial_stride = gate_up.shape[0], gate_up.shape[1] * gate_up.shape[2]
+        first = gate_up[0]
+    else:
+        _need(gate_up, "gate_up", dims=2)
+        first = gate_up
+    if first.shape != (rows, 2 * width):
+        raise KernelError("gated_act_mul: input must be [rows, 2*width]")
+    L = lib("basic.cu")
+    esz = gate_up.element_size()
+    build.check(L, L.mlb_gated_act_mul(gate_up.data_ptr(), gate_up.data_ptr() + width * esz, 2 * width, dtype_tag(gate_up),
+                                       n_partials, partial_stride, out.data_ptr(), dtype_tag(out), rows, width,
+                                       ACTIVATIONS[activation], _stream()))
+
+
 def cast_f32_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
     _need(x, "x", torch.float32); _need(out, "out", torch.bfloat16)
     if x.numel() != out.numel():
@@ -303,6 +337,49 @@ def copy_raw(dst: int, src: int, nbytes: int, to_device: bool) -> None:
     status = L.mlb_copy_async(dst, src, nbytes, 1 if to_device else 0, _stream())
     if status != 0:
         build.check(L, status)
+
+
+# ------------------------------------------------------------------------------ layer norm
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor,
+              rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = (v - mean) / sqrt(var + eps) * weight + bias with v = x[rows[r]] if rows is given else x[r]; fp32 math."""
+    _need(x, "x", torch.float32, 2); _need(weight, "weight", torch.float32, 1); _need(bias, "bias", torch.float32, 1)
+    _need(out, "out", dims=2)
+    width = x.shape[1]
+    n = rows.shape[0] if rows is not None else x.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+    if weight.shape[0] != width or bias.shape[0] != width or out.shape != (n, width):
+        raise KernelError("layernorm: shapes do not agree")
+    L = lib("layernorm.cu")
+    build.check(L, L.mlb_layernorm(x.data_ptr(), weight.data_ptr(), bias.data_ptr(), out.data_ptr(), dtype_tag(out), _ptr(rows),
+                                   n, width, float(eps), _stream()))
+
+
+def scale_add_layernorm(x: torch.Tensor, alpha: float, terms, weight: torch.Tensor, bias: torch.Tensor, eps: float,
+                        out: Optional[torch.Tensor]) -> None:
+    """x <- layernorm(alpha * x + sum_i s_i * d_i) in place (fp32), and `out` (when given) a copy of the new x in its own
+    dtype.  `terms`: one or two (s_i, d_i); a d_i may be [S, M, N] partial results, summed over S in order."""
+    _need(x, "x", torch.float32, 2); _need(weight, "weight", torch.float32, 1); _need(bias, "bias", torch.float32, 1)
+    terms = list(terms)
+    if not 1 <= len(terms) <= 2:
+        raise KernelError("scale_add_layernorm: one or two terms")
+    if weight.shape[0] != x.shape[1] or bias.shape[0] != x.shape[1]:
+        raise KernelError("scale_add_layernorm: shapes do not agree")
+    if out is not None:
+        _need(out, "out", dims=2)
+        if out.shape != x.shape:
+            raise KernelError("scale_add_layernorm: the copy must have the stream's shape")
+    args = []
+    for s, d in terms:
+        n, stride = _partials(d, x.shape, "scale_add_layernorm term")
+        args += [d.data_ptr(), n, stride, float(s)]
+    if len(terms) == 1:
+        args += [None, 0, 0, 0.0]
+    L = lib("layernorm.cu")
+    build.check(L, L.mlb_scale_add_layernorm(x.data_ptr(), float(alpha), *args, weight.data_ptr(), bias.data_ptr(), _ptr(out),
+                                             dtype_tag(out) if out is not None else F32, x.shape[0], x.shape[1], float(eps),
+                                             _stream()))
 
 
 # ------------------------------------------------------------------------------ scaled residual stream

@@ -45,6 +45,8 @@ class Attention(Mixer):
         attention_kernels.check_head_dim(self.d)
         self.rt = rt
         self.rotary = position.rotary_table(self.d) if position is not None else None
+        if self.rotary is not None and self.rotary.magnitude != 1.0:
+            raise ValueError("this mixer's rotation kernels take plain cosines and sines; use `normed_attention` for a stretched table")
         if self.rotary is None:        # no rotation: an empty table makes the kernel pass q/k through
             self._no_rot = torch.zeros(0, dtype=torch.float32, device=rt.device)
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
@@ -147,3 +149,185 @@ class Attention(Mixer):
                                           beside_mma_products=x.dtype == torch.bfloat16 and gemm_bf16.gemv_preferred(x, self.w_o))
         return linear(o, self.w_o, self.b_o, torch.float32, partials_ok=True, error_flag=ctx.error_flag,      # [T, H] f32, or its partial sums
                       alloc=lambda shape, dtype: ctx.buffer("attention.out", shape, dtype))
+
+
+@register_mixer("normed_attention")
+class NormedAttention(Mixer):
+    """Grouped-query softmax attention with the steps some designs put between projection and scores, each an option:
+
+      q, k, v = Wq x, Wk x, Wv x          `values="keys"`: there is no Wv and v is k AS PROJECTED (before norm and rotation)
+      short causal convolution over time on every channel of q, k, v (`conv` taps > 1; weights [channels, taps], the last
+          column is the current token's; the last taps - 1 projected rows of a sequence are kept in its state slot)
+      per-head rms norm of q and k with one weight each, shared by the heads (`qk_norm`)
+      rotation by the position encoding's table: any even part of the head, split-half or interleaved pairs... this
+          mixer's kernel turns interleaved pairs (2i, 2i + 1); cosines and sines times the table's magnitude
+      q times 1 + coef * ln(floor((p + 1) / every) + 1) at position p (`q_temp = (coef, every)`)
+      score = q . k * scale, causal (optionally the last `window` keys), softmax
+      concat_heads(o) * sigmoid(Wg x) (`gate`), then Wo
+
+    Keys have `dim` elements per head and values `vdim`; the cache holds both widths (`PagedKVNeed.value_dim`).  All
+    projections that read x are one fused product; norm, rotation, temperature, softmax and the gate are fp32.
+    """
+    graph_safe = True
+
+    def __init__(self, params: dict, rt: Runtime, position: Optional[PositionEncoding] = None):
+        from ..kernels import attention_kv
+        self.prefix = params.get("prefix", "")
+        self.hidden = int(params["hidden_size"])
+        self.nh, self.nkv = int(params["num_heads"]), int(params["num_kv_heads"])
+        self.dk, self.dv = int(params["dim"]), int(params.get("vdim", params["dim"]))
+        self.scale = float(params.get("scale", 1.0 / math.sqrt(float(self.dk))))
+        self.eps = float(params.get("eps", 1e-6))
+        self.values = params.get("values", "projected")
+        self.taps = int(params.get("conv", 1))
+        self.has_gate = bool(params.get("gate", False))
+        self.qk_norm = bool(params.get("qk_norm", True))
+        self.q_temp = tuple(params["q_temp"]) if params.get("q_temp") else None
+        self.window = params.get("window")
+        if self.values not in ("projected", "keys"):
+            raise ValueError(f"normed_attention: values {self.values!r} is not 'projected' or 'keys'")
+        if self.values == "keys" and self.dv != self.dk:
+            raise ValueError("normed_attention: values that are the projected keys have the keys' width")
+        if self.nh % self.nkv:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        attention_kv.check_widths(self.dk, self.dv)
+        names = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_norm="q_norm.weight",
+                     k_norm="k_norm.weight", gate="g_proj.weight", q_conv="q_conv.weight", k_conv="k_conv.weight",
+                     v_conv="v_conv.weight")
+        names.update(params.get("names", {}))
+        self.names = names
+        self.rt = rt
+        table = position.rotary_table(self.dk) if position is not None else None
+        if table is not None and not table.interleaved:
+            raise ValueError("normed_attention turns interleaved pairs (2i, 2i + 1)")
+        self.freq = table.inv_freq if table is not None else None
+        self.rot_dims = table.rotary_dim if table is not None else 0
+        self.magnitude = table.magnitude if table is not None else 1.0
+        # columns of the fused input projection: q | k | v (if projected) | gate (if any)
+        self.q_cols, self.k_cols = self.nh * self.dk, self.nkv * self.dk
+        self.v_cols = self.nkv * self.dv if self.values == "projected" else 0
+        self.g_cols = self.nh * self.dv if self.has_gate else 0
+        self.conv_cols = self.q_cols + self.k_cols + self.v_cols
+        self.w_in = self.w_o = self.q_norm_w = self.k_norm_w = self.w_conv = None
+
+    # --- declarations -----------------------------------------------------------------
+    def cache_need(self):
+        from .base import CompositeNeed, FixedStateNeed
+        kv = PagedKVNeed(self.nkv, self.dk, self.window, value_dim=self.dv)
+        if self.taps <= 1:
+            return kv
+        return CompositeNeed((("kv", kv), ("conv", FixedStateNeed((self.taps - 1, self.conv_cols), torch.float32))))
+
+    def _pieces(self):
+        n = self.names
+        pieces = [(n["q"], 0), (n["k"], self.q_cols)]
+        if self.v_cols:
+            pieces.append((n["v"], self.q_cols + self.k_cols))
+        if self.has_gate:
+            pieces.append((n["gate"], self.conv_cols))
+        return pieces
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        n = self.names
+        specs = {n["q"]: WeightSpec((self.q_cols, self.hidden)), n["k"]: WeightSpec((self.k_cols, self.hidden)),
+                 n["o"]: WeightSpec((self.hidden, self.nh * self.dv))}
+        if self.v_cols:
+            specs[n["v"]] = WeightSpec((self.v_cols, self.hidden))
+        if self.has_gate:
+            specs[n["gate"]] = WeightSpec((self.g_cols, self.hidden))
+        if self.qk_norm:
+            specs[n["q_norm"]] = WeightSpec((self.dk,), role="vector", init=("one_plus_normal", 0.1))
+            specs[n["k_norm"]] = WeightSpec((self.dk,), role="vector", init=("one_plus_normal", 0.1))
+        if self.taps > 1:
+            for key, cols in (("q_conv", self.q_cols), ("k_conv", self.k_cols), ("v_conv", self.v_cols)):
+                if cols:
+                    specs[n[key]] = WeightSpec((cols, self.taps), role="vector", init=("normal", 0.5))
+        return specs
+
+    def fused_tensors(self):
+        fused = {"in_proj.weight": (WeightSpec((self.conv_cols + self.g_cols, self.hidden)), self._pieces())}
+        if self.taps > 1:
+            n = self.names
+            rows = [(n["q_conv"], 0), (n["k_conv"], self.q_cols)] + ([(n["v_conv"], self.q_cols + self.k_cols)] if self.v_cols else [])
+            fused["conv.weight"] = (WeightSpec((self.conv_cols, self.taps), role="vector"), rows)
+        return fused
+
+    def kernel_sources(self):
+        from ..kernels import attention_kv, recurrent
+        own = attention_kv.sources() + (recurrent.conv_sources() if self.taps > 1 else [])
+        if self.rt.is_fp32:
+            return own
+        own += gemm_bf16.sources(engine_only=True)
+        if self.dk == self.dv:
+            own += attention_kernels.mma_sources(self.dk) + attention_kernels.tc_sources(self.dk)
+        return own
+
+    def bind(self, tensors):
+        n = self.names
+        if "in_proj.weight" in tensors:
+            self.w_in = tensors["in_proj.weight"]
+        else:
+            self.w_in = torch.cat([tensors[name] for name, _ in self._pieces()], 0).contiguous()
+        if self.taps > 1:
+            if "conv.weight" in tensors:
+                self.w_conv = tensors["conv.weight"]
+            else:
+                keys = ["q_conv", "k_conv"] + (["v_conv"] if self.v_cols else [])
+                self.w_conv = torch.cat([tensors[n[k]] for k in keys], 0).contiguous()
+        self.w_o = tensors[n["o"]]
+        self.q_norm_w = tensors[n["q_norm"]] if self.qk_norm else None
+        self.k_norm_w = tensors[n["k_norm"]] if self.qk_norm else None
+
+    def replay_key(self):
+        if not self.rt.is_fp32 and not gemm_bf16._direct_library(self.rt.device):
+            return None
+        rotary = None if self.freq is None else (self.freq.data_ptr(), self.rot_dims, self.magnitude)
+        return ("normed_attention", self.hidden, self.nh, self.nkv, self.dk, self.dv, self.scale, self.eps, self.values, self.taps,
+                self.has_gate, self.qk_norm, self.q_temp, self.window, rotary)
+
+    def own_tensors(self):
+        return [self.w_in, self.w_o, self.q_norm_w, self.k_norm_w, self.w_conv]
+
+    def _shared_kernels(self, page_size: int) -> bool:
+        """Whether the attention itself can run on the kernels of equal key and value widths."""
+        return (self.dk == self.dv and not self.rt.is_fp32 and attention_kernels.mma_supported(self.dk, page_size))
+
+    def plan_stale(self, ctx: StepContext, max_seq_len: int) -> bool:
+        from ..kernels.device import sm_count
+        return attention_kernels.decode_plan_stale(ctx, max_seq_len, sm_count(self.rt.device))
+
+    def forget_plans(self, ctx: StepContext) -> None:
+        attention_kernels.forget_plans(ctx)
+
+    def plan_group(self):
+        return ("attention", self.rt.device)
+
+    # --- compute ------------------------------------------------------------------------
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
+        from ..kernels import attention_kv, recurrent
+        T, dt, flag = x.shape[0], self.rt.dtype, ctx.error_flag
+        kv_view = cache["kv"] if isinstance(cache, dict) else cache
+        proj = linear(x, self.w_in, None, torch.float32, partials_ok=True, error_flag=flag,
+                      alloc=lambda shape, dtype: ctx.buffer("normed_attention.proj", shape, dtype))
+        src, q_col, k_col = proj, 0, self.q_cols
+        v_col = self.q_cols + self.k_cols if self.v_cols else k_col
+        if self.taps > 1:
+            state = cache["conv"]
+            src = ctx.buffer("normed_attention.conv", (T, self.conv_cols), torch.float32)
+            recurrent.short_conv(proj, 0, self.w_conv, state.storage, state.slots, ctx, src, silu=False, update_state=state.writable)
+        q = ctx.buffer("normed_attention.q", (T, self.q_cols), dt)
+        attention_kv.qk_prepare(src, q_col, k_col, v_col, q_norm=self.q_norm_w, k_norm=self.k_norm_w, eps=self.eps, freq=self.freq,
+                                rot_dims=self.rot_dims, magnitude=self.magnitude, q_temp=self.q_temp, positions=ctx.positions,
+                                token_seq=ctx.token_seq, block_table=kv_view.block_table,
+                                pages=kv_view.pages if kv_view.writable else None, page_size=kv_view.page_size, q_out=q,
+                                heads=self.nh, kv_heads=self.nkv, dk=self.dk, dv=self.dv, error_flag=flag)
+        o = ctx.buffer("normed_attention.o", (T, self.nh * self.dv), dt)
+        if self._shared_kernels(kv_view.page_size) and not self.has_gate:
+            attention_kernels.paged_attention(q, kv_view.pages, o, ctx, kv_view.block_table, self.nh, self.nkv, self.dk, self.scale,
+                                              self.window, beside_mma_products=gemm_bf16.gemv_preferred(x, self.w_o))
+        else:
+            attention_kv.paged_attention_kv(q, kv_view.pages, o, ctx.positions, ctx.token_seq, kv_view.block_table, kv_view.page_size,
+                                            self.nh, self.nkv, self.dk, self.dv, self.scale, self.window,
+                                            proj if self.has_gate else None, self.conv_cols, flag)
+        return linear(o, self.w_o, None, torch.float32, partials_ok=True, error_flag=flag,
+                      alloc=lambda shape, dtype: ctx.buffer("normed_attention.out", shape, dtype))

@@ -60,11 +60,14 @@ class WeightSpec:
 class PagedKVNeed:
     """Keys and values that grow with the tokens.  `window`: only the last `window` keys are
     ever read (pages behind it may be given back while the request lives); None: all keys.
-    `dtype`: what the pages store; None: the runtime's compute dtype."""
+    `dtype`: what the pages store; None: the runtime's compute dtype.  `value_dim`: width of a value when it
+    differs from a key's (None: head_dim); a page then holds the keys of all kv heads [NKV, page_size, head_dim]
+    followed by the values [NKV, page_size, value_dim], which for equal widths is the same bytes as [2, NKV, page_size, D]."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     dtype: Optional[torch.dtype] = None
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -83,9 +86,36 @@ class FixedStateNeed:
     dtype: torch.dtype = torch.float32
 
 
+@dataclass(frozen=True)
+class CompositeNeed:
+    """Several caches for one mixer (keys and values in pages beside a fixed-size state, say): sub-name -> need.
+    The model makes one cache entry per item, named `<run's cache name>.<sub-name>`, and the mixer's forward gets a
+    dict sub-name -> view.  Items may themselves be composite (a mixer made of mixers)."""
+    items: Tuple[Tuple[str, Any], ...]
+
+    def flat(self, prefix: str = "") -> List[Tuple[str, Any]]:
+        out: List[Tuple[str, Any]] = []
+        for name, need in self.items:
+            if need is None:
+                continue
+            if isinstance(need, CompositeNeed):
+                out += need.flat(prefix + name + ".")
+            else:
+                out.append((prefix + name, need))
+        return out
+
+
+def sub_views(views: Dict[str, Any], name: str) -> Any:
+    """What a sub-mixer `name` of a mixer with a CompositeNeed gets: its own view, or the dict of those below it."""
+    if name in views:
+        return views[name]
+    below = {k[len(name) + 1:]: v for k, v in views.items() if k.startswith(name + ".")}
+    return below or None
+
+
 @dataclass
 class PagedKVView:
-    pages: torch.Tensor            # [num_pages, 2, NKV, page_size, D]; for a PagedRowsNeed [num_pages, page_size, width]
+    pages: torch.Tensor            # [num_pages, 2, NKV, page_size, D] (value_dim set and different: [num_pages, NKV * page_size * (D + DV)]); for a PagedRowsNeed [num_pages, page_size, width]
     block_table: torch.Tensor      # [A, max_blocks] int32, this step's sequences, this group
     page_size: int
     writable: bool                 # False: the run reads a cache another run wrote
@@ -207,6 +237,7 @@ class RotaryTable:
     inv_freq: torch.Tensor         # [rotary_dim/2] f32 on the device
     rotary_dim: int
     interleaved: bool
+    magnitude: float = 1.0         # factor on every cosine and sine (stretched frequencies come with one)
 
 
 class PositionEncoding(Part):

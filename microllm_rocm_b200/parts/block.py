@@ -102,3 +102,51 @@ class PreNormResidualBlock(Block):
         scaled.zero_()
         ops.add_scaled_inplace(scaled, out, self.a2)
         return residual, scaled
+
+
+@register_block("post_norm_residual")
+class PostNormResidualBlock(Block):
+    """Norm after the sum:  x <- norm1(alpha * x + mixer(x));  x <- norm2(alpha * x + feed_forward(x)).  The sublayers read
+    the stream itself, so the stream that leaves a block is final (no delta is handed on) and, on the bf16 path, travels
+    with a bf16 copy for the products that read it; the sums and norms are fp32.  A mixer that is several mixers side
+    by side may hand over its weighted terms (`forward_terms`): the norm kernel adds them, no pass of its own."""
+    carries_no_delta = True
+
+    def __init__(self, params: dict, rt: Runtime, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, feed_forward: FeedForward):
+        self.rt = rt
+        self.prefix = params.get("prefix", "")
+        self.alpha = float(params.get("alpha", 1.0))
+        self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward = mixer_norm, mixer, ffn_norm, feed_forward
+        self.has_ff = not getattr(feed_forward, "absent", False)
+        for norm in (mixer_norm, ffn_norm) if self.has_ff else (mixer_norm,):
+            if not hasattr(norm, "post_forward"):
+                raise TypeError("post_norm_residual needs norms that can normalise a scaled sum in place (post_forward)")
+
+    def replay_key(self):
+        keys = [p.replay_key() for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)]
+        return None if any(k is None for k in keys) else ("post_norm_residual", self.rt.dtype, self.alpha, *keys)
+
+    def own_tensors(self):
+        return [t for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) for t in p.own_tensors()]
+
+    def _reads(self, stream: torch.Tensor, ctx: StepContext):
+        """What the sublayers' products read: the stream itself (fp32 path) or its bf16 copy."""
+        if self.rt.is_fp32:
+            return stream, None
+        return None, ctx.buffer("block.stream_copy", tuple(stream.shape), self.rt.dtype)
+
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext, cache):
+        if delta is not None:            # a block of another arrangement ran before this one
+            ops.add_inplace(residual, delta)
+        x, copy = self._reads(residual, ctx)
+        if x is None:
+            x = copy
+            if ctx.step_values.get("block.stream_copy_of") != residual.data_ptr():
+                ops.cast_f32_bf16(residual, copy)            # the first block of a step: nobody has made the copy yet
+        terms = self.mixer.forward_terms(x, ctx, cache) if hasattr(self.mixer, "forward_terms") else [(1.0, self.mixer.forward(x, ctx, cache))]
+        self.mixer_norm.post_forward(residual, self.alpha, terms, copy)
+        if self.has_ff:
+            self.ffn_norm.post_forward(residual, self.alpha, [(1.0, self.feed_forward.forward(x, ctx))], copy)
+        if copy is not None:
+            ctx.step_values["block.stream_copy_of"] = residual.data_ptr()
+        return residual, None

@@ -14,8 +14,8 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..config.spec import ModelSpec
-from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, RUN_ENTRIES, Part, Runtime,
-                   StepContext, WeightSpec, make)
+from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, RUN_ENTRIES, CompositeNeed, Part,
+                   Runtime, StepContext, WeightSpec, make)
 
 
 @dataclass
@@ -66,6 +66,7 @@ class Model:
         # caches: one entry per owning run
         self.cache_entries: Dict[str, CacheEntry] = {}
         self.run_cache: List[Tuple[Optional[str], bool]] = []    # per run: (cache name, owns it)
+        self.run_cache_parts: Dict[str, List[str]] = {}          # cache name of a run whose mixer keeps several caches -> sub-names
         for i, run in enumerate(spec.order):
             need = self.blocks[run.layer].mixer.cache_need()
             if need is None:
@@ -73,6 +74,19 @@ class Model:
                 continue
             name = spec.cache_name(i)
             owns = run.read_cache_of is None
+            if isinstance(need, CompositeNeed):
+                # one entry per item, `<name>.<sub-name>`; the mixer gets a dict of views
+                flat = need.flat()
+                if owns:
+                    if name in self.run_cache_parts:
+                        raise ValueError(f"two runs own the cache {name!r}")
+                    for sub, item in flat:
+                        self.cache_entries[f"{name}.{sub}"] = CacheEntry(f"{name}.{sub}", item)
+                    self.run_cache_parts[name] = [sub for sub, _ in flat]
+                elif self.run_cache_parts.get(name) != [sub for sub, _ in flat]:
+                    raise ValueError(f"order[{i}] reads cache {name!r} of another kind than its mixer needs")
+                self.run_cache.append((name, owns))
+                continue
             if owns:
                 if name in self.cache_entries:
                     raise ValueError(f"two runs own the cache {name!r}")
@@ -109,8 +123,9 @@ class Model:
                 name, owns = self.run_cache[i]
                 group = None
                 if name is not None:
-                    need = self.cache_entries[name].need
-                    group = (type(need).__name__, getattr(need, "window", None), getattr(need, "dtype", None))
+                    needs = [self.cache_entries[f"{name}.{sub}"].need for sub in self.run_cache_parts[name]] \
+                        if name in self.run_cache_parts else [self.cache_entries[name].need]
+                    group = tuple((type(need).__name__, getattr(need, "window", None), getattr(need, "dtype", None)) for need in needs)
                 keys.append(None if key is None else (key, owns, group))
             self._replay_keys = keys
         return self._replay_keys
@@ -202,13 +217,18 @@ class Model:
             name, owns = self.run_cache[i]
             view = None
             if name is not None:
-                view = caches[name]
-                if not owns:
-                    view = _read_only(view)
+                if name in self.run_cache_parts:
+                    view = {sub: caches[f"{name}.{sub}"] if owns else _read_only(caches[f"{name}.{sub}"])
+                            for sub in self.run_cache_parts[name]}
+                else:
+                    view = caches[name]
+                    if not owns:
+                        view = _read_only(view)
             block = self.blocks[run.layer]
             if self.run_entries[i] is not None:
                 self.run_entries[i].forward(residual, ctx, embedding_output)
-            key = keys[i] if keys is not None and i > 0 and delta is not None else None
+            # (a block that normalises after its sums hands no delta on: then none comes in and none goes out)
+            key = keys[i] if keys is not None and i > 0 and (delta is not None or getattr(block, "carries_no_delta", False)) else None
             if key is None:
                 # the first run of a step plans launches and makes the step's tables: it always runs call by call
                 residual, delta = block.forward(residual, delta, ctx, view)
@@ -222,8 +242,9 @@ class Model:
                 with Recorder() as recorder:
                     out_residual, out_delta = block.forward(residual, delta, ctx, view)
                 recording = None
-                if (out_residual is residual and out_delta is not None and delta is not None
-                        and out_delta.data_ptr() == delta.data_ptr() and recorder.unrecordable is None):
+                same_delta = (out_delta is None and delta is None) or (
+                    out_delta is not None and delta is not None and out_delta.data_ptr() == delta.data_ptr())
+                if out_residual is residual and same_delta and recorder.unrecordable is None:
                     recording = Recording(recorder)
                     if not _swappable(recording, block, view):
                         recording = None
@@ -255,6 +276,8 @@ class Model:
 def _view_tensors(view) -> List[Optional[torch.Tensor]]:
     if view is None:
         return []
+    if isinstance(view, dict):
+        return [t for sub in view.values() for t in _view_tensors(sub)]
     return [getattr(view, "pages", None), getattr(view, "storage", None)]
 
 

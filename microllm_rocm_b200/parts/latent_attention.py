@@ -50,6 +50,8 @@ class LatentAttention(Mixer):
         latent.check_sizes(self.rank, self.rot_dim)
         self.rt = rt
         table = position.rotary_table(self.rot_dim) if position is not None and self.rot_dim else None
+        if table is not None and table.magnitude != 1.0:
+            raise ValueError("latent attention takes plain cosines and sines")
         if table is not None and table.interleaved:
             raise ValueError("latent attention pairs element i with i + rotary_dim / 2")
         self.inv_freq = table.inv_freq if table is not None else torch.zeros(0, dtype=torch.float32, device=rt.device)

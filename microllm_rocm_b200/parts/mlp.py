@@ -1,6 +1,6 @@
-"""SwiGLU feed-forward: down( silu(gate(x)) * up(x) ), no biases
-(reference: src/model/model.cpp:757-794; activation src/ops/ops.cpp:760-785).
-Gate and up are one fused product (gate rows first, then up rows)."""
+"""Gated feed-forward: down( act(gate(x)) * up(x) ), no biases; act = silu (SwiGLU, the default;
+reference: src/model/model.cpp:757-794; activation src/ops/ops.cpp:760-785) or the tanh form of gelu
+(`activation="gelu_tanh"`).  Gate and up are one fused product (gate rows first, then up rows)."""
 from __future__ import annotations
 
 from typing import Dict
@@ -20,6 +20,9 @@ class SwiGLU(FeedForward):
         self.inter = int(params["intermediate_size"])
         # local names of the three matrices in the checkpoint (gate, up, down)
         self.n_gate, self.n_up, self.n_down = params.get("names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
+        self.activation = params.get("activation", "silu")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"feed-forward activation {self.activation!r} is not one of {', '.join(ops.ACTIVATIONS)}")
         self.rt = rt
         self.w_gate_up = self.w_down = None
 
@@ -45,7 +48,7 @@ class SwiGLU(FeedForward):
     def replay_key(self):
         if not self.rt.is_fp32 and not gemm_bf16._direct_library(self.rt.device):
             return None                  # the library product would go through the tensor framework
-        return ("swiglu", self.hidden, self.inter)
+        return ("swiglu", self.hidden, self.inter, self.activation)
 
     def own_tensors(self):
         return [self.w_gate_up, self.w_down]
@@ -56,7 +59,12 @@ class SwiGLU(FeedForward):
         # boundary -- the reference's policy for its bf16 feed-forward (src/ops/optimized.cpp:676-683).
         act = scratch(ctx, "swiglu.act", (x.shape[0], self.inter), self.rt.dtype, x.device)
         flag = ctx.error_flag if ctx is not None else None      # one flag covers the step: whoever reads it sees every kernel's
-        if (x.dtype == torch.bfloat16 and x.shape[0] <= gemm_bf16.GEMV_SILU_MAX_TOKENS and gemm_bf16.gemv_preferred(x, self.w_gate_up)
+        if self.activation != "silu":
+            # the fused epilogues are SiLU's: product, then the activation as a kernel of its own
+            gate_up = linear(x, self.w_gate_up, None, torch.float32 if self.rt.is_fp32 else self.rt.dtype, partials_ok=not self.rt.is_fp32,
+                             error_flag=flag, alloc=lambda shape, dtype: scratch(ctx, "swiglu.gate_up", shape, dtype, x.device))
+            ops.gated_act_mul(gate_up, act, self.activation)
+        elif (x.dtype == torch.bfloat16 and x.shape[0] <= gemm_bf16.GEMV_SILU_MAX_TOKENS and gemm_bf16.gemv_preferred(x, self.w_gate_up)
                 and gemm_bf16.gemv_fused_supported(x, self.w_gate_up)):
             # a few tokens: one weight-streaming kernel, the activation is its epilogue
             gemm_bf16.gemv_silu_mul(x, self.w_gate_up, act)

@@ -1,5 +1,7 @@
 """RMSNorm: y = x * (1 / sqrt(mean(x^2) + eps)) * w, all in fp32
-(reference: src/ops/ops.cpp:684-699; fused with the residual add at :702-740)."""
+(reference: src/ops/ops.cpp:684-699; fused with the residual add at :702-740).
+LayerNorm: y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b, all in fp32; besides the plain form it offers the
+step of a block that normalises AFTER its sums: x <- norm(alpha * x + weighted results), in place."""
 from __future__ import annotations
 
 from typing import Dict, Optional
@@ -44,3 +46,52 @@ class RMSNorm(Norm):
             ops.add_scaled_rmsnorm(residual, delta, scale, self.weight, self.eps, out)
         else:
             ops.add_rmsnorm(residual, delta, self.weight, self.eps, out)
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    def __init__(self, params: dict, rt: Runtime):
+        self.prefix = params.get("prefix", "")
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.name = params.get("name", "weight")
+        self.bias_name = params.get("bias_name", "bias")
+        self.absent = bool(params.get("absent", False))
+        self.rt = rt
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        if self.absent:
+            return {}
+        return {self.name: WeightSpec((self.size,), role="vector", init=("one_plus_normal", 0.1)),
+                self.bias_name: WeightSpec((self.size,), role="vector", init=("normal", 0.1))}
+
+    def kernel_sources(self):
+        return [("layernorm.cu", {})]
+
+    def bind(self, tensors):
+        self.weight, self.bias = tensors.get(self.name), tensors.get(self.bias_name)
+        if not self.absent and (self.weight is None or self.bias is None):
+            raise KeyError(f"layer norm: {self.name} or {self.bias_name} is missing")
+
+    def replay_key(self):
+        return ("layernorm", self.size, self.eps)
+
+    def own_tensors(self):
+        return [self.weight, self.bias]
+
+    def forward(self, x, out, rows=None):
+        ops.layernorm(x, self.weight, self.bias, self.eps, out, rows=rows)
+
+    def add_forward(self, residual, delta, out, scale=None):
+        # the pre-norm use (residual += delta, then a normed copy) has no kernel of its own yet: two steps
+        if scale is not None:
+            ops.add_scaled_inplace(residual, delta, scale)
+        else:
+            ops.add_inplace(residual, delta)
+        ops.layernorm(residual, self.weight, self.bias, self.eps, out)
+
+    def post_forward(self, stream: torch.Tensor, alpha: float, terms, copy: Optional[torch.Tensor]) -> None:
+        """stream <- norm(alpha * stream + sum_i s_i * d_i) in place (fp32); `copy` receives the new stream in its dtype."""
+        ops.scale_add_layernorm(stream, alpha, terms, self.weight, self.bias, self.eps, copy)

@@ -7,8 +7,16 @@ The reference recomputes it inside every kernel call; here it is computed once. 
 src/model/config.h:9), 'interleaved' pairs 2i with 2i+1.  `rotary_dim` smaller than the
 head size leaves the remaining elements untouched.  Optional `scale` divides positions'
 frequencies (linear scaling); it defaults to 1.
+
+Optional `stretch` {factor, original, fast, slow} stretches the slow frequencies for contexts longer than `original`
+positions: with where(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta) (the pair index whose wave makes t turns
+over `original` positions), lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), rotary_dim - 1) and
+ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns with f_i / factor * ramp_i + f_i * (1 - ramp_i), and
+every cosine and sine is multiplied by 0.1 * ln(factor) + 1 (`RotaryTable.magnitude`).
 """
 from __future__ import annotations
+
+import math
 
 import numpy as np
 import torch
@@ -25,6 +33,22 @@ def inverse_frequencies(theta: float, rotary_dim: int, scale: float = 1.0) -> np
     return inv
 
 
+def stretched_frequencies(theta: float, rotary_dim: int, stretch: dict):
+    """(inverse frequencies [rotary_dim/2] fp32, factor on cos and sin) of the stretched table; float64 on the host."""
+    factor, original = float(stretch["factor"]), float(stretch["original"])
+    if not (factor > 0 and original > 0 and float(stretch["fast"]) > 0 and float(stretch["slow"]) > 0 and theta != 1.0):
+        raise ValueError("rotary stretch: factor, original, fast and slow must be positive")
+    where = lambda turns: rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+    lo = max(math.floor(where(float(stretch["fast"]))), 0)
+    hi = min(math.ceil(where(float(stretch["slow"]))), rotary_dim - 1)
+    out = np.zeros(rotary_dim // 2, dtype=np.float64)
+    for i in range(rotary_dim // 2):
+        f = float(theta) ** (-2.0 * i / rotary_dim)
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out[i] = f / factor * ramp + f * (1.0 - ramp)
+    return out.astype(np.float32), 0.1 * math.log(factor) + 1.0
+
+
 @register_position_encoding("rotary")
 class RotaryEmbedding(PositionEncoding):
     def __init__(self, params: dict, rt: Runtime):
@@ -39,9 +63,13 @@ class RotaryEmbedding(PositionEncoding):
             raise ValueError("rotary_dim must be even and at most head_dim")
         if not self.theta > 0:
             raise ValueError("rotary theta must be positive")
-        inv = inverse_frequencies(self.theta, self.rotary_dim, self.scale)
+        magnitude = 1.0
+        if params.get("stretch"):
+            inv, magnitude = stretched_frequencies(self.theta, self.rotary_dim, params["stretch"])
+        else:
+            inv = inverse_frequencies(self.theta, self.rotary_dim, self.scale)
         self._table = RotaryTable(torch.from_numpy(inv).to(rt.device), self.rotary_dim,
-                                  self.layout == "interleaved")
+                                  self.layout == "interleaved", magnitude)
 
     def rotary_table(self, head_dim: int):
         if head_dim != self.head_dim:
