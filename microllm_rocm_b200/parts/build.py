@@ -234,7 +234,8 @@ class Model:
                 residual, delta = block.forward(residual, delta, ctx, view)
                 if sink is not None:
                     sink(f"run{i}.layer{run.layer}.residual", residual)
-                    sink(f"run{i}.layer{run.layer}.delta", delta)
+                    if delta is not None:            # a block that normalises after its sums hands none on
+                        sink(f"run{i}.layer{run.layer}.delta", delta)
                 continue
             pointers = self._run_pointers(block, view)
             if key not in recordings:
