@@ -1,0 +1,387 @@
+"""The Matidra decoder on the GPU against its plain float64 restatement: each mechanism alone, then whole models cut in
+every way (whole prompts, a tail decoded token by token, portions down to two tokens, mixed batches over a pool so small
+that pages and state slots are used again), in true fp32 and in bf16, and greedy generation through the scheduler."""
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from tests.helpers import collect, random_tokens, steps_mixed, steps_portions, steps_prefill_then_decode, steps_whole
+from tests.matidra_cases import CASES, case, write_folder
+from tests.plain import matidra_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 3e-5          # of the largest |logit|
+BF16_TOL = 0.04          # of the largest |logit|
+DEV = "cuda:0"
+LENGTHS = {"a": [1, 2, 37, 130], "b": [5, 64, 99], "c": [3, 50, 290], "d": [17, 80]}
+
+
+def tol(dtype):
+    return FP32_TOL if dtype == "float32" else BF16_TOL
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for key in CASES:
+        raw, weights = case(key)
+        out[key] = (write_folder(str(tmp_path_factory.mktemp("matidra_" + key)), raw, weights), raw, weights)
+    return out
+
+
+def engine_for(folder, dtype, max_tokens=1024, page_size=16, max_requests=4):
+    from microllm_rocm_b200.engine.loading import load_engine
+    return load_engine(folder, dtype=dtype, page_size=page_size, max_tokens=max_tokens, max_requests=max_requests)
+
+
+_plain = {}
+
+
+def plain_logits(raw, weights, tokens):
+    k = (id(weights), tuple(tokens))
+    if k not in _plain:
+        _plain[k] = plain.forward(raw, weights, list(tokens)).float()
+    return _plain[k]
+
+
+def compare(got, key, raw, weights, requests, dtype):
+    worst = 0.0
+    for rid, toks in requests.items():
+        ref = plain_logits(raw, weights, toks)
+        rows = torch.stack([got[(rid, p)] for p in range(len(toks))])
+        assert torch.isfinite(rows).all(), f"case {key} request {rid}: logits that are not finite"
+        err = (rows - ref).abs().amax(dim=1) / ref.abs().max()
+        over = err > tol(dtype)
+        if over.any():
+            pos = int(over.nonzero()[0])
+            raise AssertionError(f"case {key} request {rid}: {int(over.sum())} positions over the tolerance {tol(dtype)}, the first "
+                                 f"is {pos} of {len(toks)} (error {float(err[pos]):.3e} of the largest |logit|)")
+        worst = max(worst, float(err.max()))
+    print(f"[matidra parity] case {key} {dtype}: worst error {worst:.3e} of the largest |logit|")
+    return worst
+
+
+def requests_for(raw, lengths, seed=0):
+    return {f"r{i}": random_tokens(n, raw["vocab"], seed + 100 * i + n) for i, n in enumerate(lengths)}
+
+
+def step_of(lengths, pos0, slots):
+    """The per-sequence arrays a kernel sees of a step whose sequences bring `lengths` tokens from positions `pos0`."""
+    starts = [0]
+    for n in lengths:
+        starts.append(starts[-1] + n)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    return SimpleNamespace(
+        seq_starts=i32(starts), seq_pos0=i32(pos0), num_seqs=len(lengths), error_flag=torch.zeros(1, dtype=torch.int32, device=DEV),
+        token_seq=i32([a for a, n in enumerate(lengths) for _ in range(n)]),
+        positions=i32([p + i for p, n in zip(pos0, lengths) for i in range(n)])), i32(slots)
+
+
+# ------------------------------------------------------------------------------------------- mechanisms alone
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_layer_norm_plain_and_after_a_weighted_sum(out_dtype):
+    from microllm_rocm_b200.kernels import ops
+    torch.manual_seed(1)
+    for width in (40, 257, 1024):
+        x = torch.randn(9, width, device=DEV) * 3 + 1
+        w, b = torch.randn(width, device=DEV), torch.randn(width, device=DEV)
+        rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+        out = torch.empty(3, width, dtype=out_dtype, device=DEV)
+        ops.layernorm(x, w, b, 1e-5, out, rows=rows)
+        want = plain.layer_norm(x.double()[rows.long()], w.double(), b.double(), 1e-5)
+        assert torch.allclose(out.double(), want, atol=1e-5 if out_dtype == torch.float32 else 0.05)
+        d1, d2 = torch.randn(3, 9, width, device=DEV), torch.randn(9, width, device=DEV)          # three partial sums; one plain term
+        stream, copy = x.clone(), torch.empty(9, width, dtype=out_dtype, device=DEV)
+        ops.scale_add_layernorm(stream, 2.5, [(0.6, d1), (1.1, d2)], w, b, 1e-5, copy)
+        want = plain.layer_norm(2.5 * x.double() + 0.6 * d1.double().sum(0) + 1.1 * d2.double(), w.double(), b.double(), 1e-5)
+        assert torch.allclose(stream.double(), want, atol=2e-5)
+        assert torch.allclose(copy.double(), want, atol=1e-5 if out_dtype == torch.float32 else 0.05)
+        one = x.clone()
+        ops.scale_add_layernorm(one, 1.0, [(1.0, d2)], w, b, 1e-5, None)
+        assert torch.allclose(one.double(), plain.layer_norm(x.double() + d2.double(), w.double(), b.double(), 1e-5), atol=2e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_activation_with_the_tanh_form_of_gelu(dtype):
+    from microllm_rocm_b200.kernels import ops
+    torch.manual_seed(2)
+    for rows, width in ((5, 24), (33, 100)):
+        gate_up = (torch.randn(rows, 2 * width, device=DEV) * 3).to(dtype)
+        out = torch.empty(rows, width, dtype=dtype, device=DEV)
+        ops.gated_act_mul(gate_up, out, "gelu_tanh")
+        g, u = gate_up.double()[:, :width], gate_up.double()[:, width:]
+        assert torch.allclose(out.double(), plain.gelu_tanh(g) * u, atol=1e-5 if dtype == torch.float32 else 0.08, rtol=0 if dtype == torch.float32 else 0.01)
+        silu = torch.empty_like(out)
+        ops.gated_act_mul(gate_up, silu, "silu")
+        assert not torch.allclose(silu.double(), out.double(), atol=0.05)             # the choice is not ignored
+    parts = torch.randn(3, 4, 2 * 8, device=DEV)
+    out = torch.empty(4, 8, device=DEV)
+    ops.gated_act_mul(parts, out, "gelu_tanh")
+    s = parts.double().sum(0)
+    assert torch.allclose(out.double(), plain.gelu_tanh(s[:, :8]) * s[:, 8:], atol=1e-5)
+
+
+@pytest.mark.parametrize("taps", [2, 4, 7])
+def test_short_convolution_over_steps_with_slots_used_again(taps):
+    """Three sequences through three steps of unequal portions (also shorter than the taps), the state in slots that
+    held another sequence before; against the plain convolution of each whole sequence."""
+    from microllm_rocm_b200.kernels import recurrent
+    torch.manual_seed(taps)
+    C, col0, width = 10, 3, 20
+    w = torch.randn(C, taps, device=DEV)
+    seqs = [torch.randn(n, width, device=DEV) for n in (19, 5, 11)]
+    state = torch.full((4, taps - 1, C), 777.0, device=DEV)                        # what an earlier request left in the slots
+    cuts = [[(0, 7), (7, 8), (8, 19)], [(0, 1), (1, 3), (3, 5)], [(0, 2), (2, 9), (9, 11)]]
+    got = [torch.empty(len(s), C, device=DEV) for s in seqs]
+    for step in range(3):
+        spans = [c[step] for c in cuts]
+        ctx, slots = step_of([b - a for a, b in spans], [a for a, _ in spans], [2, 0, 3])
+        u = torch.cat([s[a:b] for s, (a, b) in zip(seqs, spans)])
+        parts = torch.stack([u * 0.25, u * 0.75])                                # as two partial sums of a split product
+        y = torch.empty(u.shape[0], C, device=DEV)
+        recurrent.short_conv(parts, col0, w, state, slots, ctx, y, silu=(taps == 4))
+        at = 0
+        for i, (a, b) in enumerate(spans):
+            got[i][a:b] = y[at:at + b - a]
+            at += b - a
+        assert int(ctx.error_flag.item()) == 0
+    for s, g in zip(seqs, got):
+        want = plain.short_convolution(s.double()[:, col0:col0 + C], w.double())
+        if taps == 4:
+            want = want * torch.sigmoid(want)
+        assert torch.allclose(g.double(), want, atol=1e-5)
+
+
+@pytest.mark.parametrize("heads, kv_heads, dk, dv, rot, every", [(3, 3, 16, 24, 0, 7), (4, 2, 32, 32, 12, 0), (2, 1, 10, 6, 10, 3), (1, 1, 136, 40, 4, 0)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_rotation_temperature_then_attention_with_two_widths(heads, kv_heads, dk, dv, rot, every, dtype):
+    """qk_prepare + the attention kernel against the plain functions: two sequences in one step, the second continuing
+    from pages an earlier step wrote; a sigmoid gate read from partial sums; scattered pages."""
+    from microllm_rocm_b200.kernels import attention_kv
+    torch.manual_seed(heads * dk + dv)
+    page, n_pages = 8, 12
+    lengths, scale = [21, 13], 0.3
+    qc, kc, vc = heads * dk, kv_heads * dk, kv_heads * dv
+    width = qc + kc + vc + heads * dv
+    seqs = [torch.randn(n, width, device=DEV) for n in lengths]
+    qn, kn = 1 + 0.2 * torch.randn(dk, device=DEV), 1 + 0.2 * torch.randn(dk, device=DEV)
+    freq, magnitude = plain.stretched_frequencies(rot, 100.0, {"factor": 3.0, "original": 16, "fast": 4.0, "slow": 1.0}) if rot else (None, 1.0)
+    freq_dev = freq.float().to(DEV) if rot else None
+    pages = torch.zeros(n_pages, kv_heads * page * (dk + dv), dtype=dtype, device=DEV)
+    table = torch.tensor([[7, 2, 9], [11, 0, 4]], dtype=torch.int32, device=DEV)
+    temp = (0.5, every) if every else None
+    outs = [[], []]
+    for spans in ([(0, 21), (0, 5)], [None, (5, 13)]):
+        live = [i for i, s in enumerate(spans) if s]
+        ctx, _ = step_of([spans[i][1] - spans[i][0] for i in live], [spans[i][0] for i in live], [0] * len(live))
+        rows = torch.cat([seqs[i][spans[i][0]:spans[i][1]] for i in live])
+        src = torch.stack([rows * 0.5, rows * 0.5])
+        T = rows.shape[0]
+        q = torch.empty(T, qc, dtype=dtype, device=DEV)
+        attention_kv.qk_prepare(src, 0, qc, qc + kc, q_norm=qn, k_norm=kn, eps=1e-5, freq=freq_dev, rot_dims=rot, magnitude=magnitude,
+                                q_temp=temp, positions=ctx.positions, token_seq=ctx.token_seq, block_table=table[live].contiguous(),
+                                pages=pages, page_size=page, q_out=q, heads=heads, kv_heads=kv_heads, dk=dk, dv=dv, error_flag=ctx.error_flag)
+        o = torch.empty(T, heads * dv, dtype=dtype, device=DEV)
+        attention_kv.paged_attention_kv(q, pages, o, ctx.positions, ctx.token_seq, table[live].contiguous(), page, heads, kv_heads, dk, dv,
+                                        scale, None, src, qc + kc + vc, ctx.error_flag)
+        assert int(ctx.error_flag.item()) == 0
+        at = 0
+        for i in live:
+            n = spans[i][1] - spans[i][0]
+            outs[i].append(o[at:at + n])
+            at += n
+    for i, s in enumerate(seqs):
+        x, T = s.double().cpu(), lengths[i]
+        pos = torch.arange(T)
+        q = plain.rms(x[:, :qc].view(T, heads, dk), 1e-5) * qn.double().cpu()
+        k = plain.rms(x[:, qc:qc + kc].view(T, kv_heads, dk), 1e-5) * kn.double().cpu()
+        if rot:
+            q, k = plain.rotate_pairs(q, pos, rot, freq, magnitude), plain.rotate_pairs(k, pos, rot, freq, magnitude)
+        if temp:
+            q = q * (1.0 + temp[0] * torch.log(torch.floor((pos.double() + 1) / temp[1]) + 1.0))[:, None, None]
+        v = x[:, qc + kc:qc + kc + vc].view(T, kv_heads, dv)
+        want = plain.causal_attention(q, k, v, scale).reshape(T, heads * dv) * torch.sigmoid(x[:, qc + kc + vc:])
+        got = torch.cat(outs[i]).double().cpu()
+        assert torch.allclose(got, want, atol=2e-5 if dtype == torch.float32 else 0.06), float((got - want).abs().max())
+
+
+def test_a_window_and_a_far_key_that_carries_the_output():
+    """One query and one key scaled up so that a single score stands out: at the far end of 300 keys, at a page's last
+    and first place, just inside a window and (left out) just outside it."""
+    from microllm_rocm_b200.kernels import attention_kv
+    torch.manual_seed(5)
+    heads, dk, dv, page, T = 2, 16, 24, 16, 300
+    for target, window, seen in ((0, None, True), (15, None, True), (16, None, True), (T - 40, 40, True), (T - 41, 40, False)):
+        k, v = torch.randn(T, heads * dk, device=DEV) * 0.1, torch.randn(T, heads * dv, device=DEV)
+        qrow = torch.randn(1, heads * dk, device=DEV)
+        k[target] = qrow[0] * 3.0                                              # the one key the last query points at
+        src = torch.cat([qrow.expand(T, -1) * 3.0, k, v], 1).contiguous()
+        ctx, _ = step_of([T], [0], [0])
+        pages = torch.zeros(20, heads * page * (dk + dv), device=DEV)
+        table = torch.arange(19, -1, -1, dtype=torch.int32, device=DEV).view(1, 20)
+        q = torch.empty(T, heads * dk, device=DEV)
+        attention_kv.qk_prepare(src, 0, heads * dk, 2 * heads * dk, q_norm=None, k_norm=None, eps=1e-5, freq=None, rot_dims=0, magnitude=1.0,
+                                q_temp=None, positions=ctx.positions, token_seq=ctx.token_seq, block_table=table, pages=pages,
+                                page_size=page, q_out=q, heads=heads, kv_heads=heads, dk=dk, dv=dv, error_flag=ctx.error_flag)
+        o = torch.empty(T, heads * dv, device=DEV)
+        attention_kv.paged_attention_kv(q, pages, o, ctx.positions, ctx.token_seq, table, page, heads, heads, dk, dv, 1.0, window, None, 0,
+                                        ctx.error_flag)
+        close = torch.allclose(o[-1], v[target], atol=1e-3)
+        assert close == seen, (target, window)
+
+
+@pytest.mark.parametrize("heads, kv_heads, dk, dv, ra, rg", [(4, 2, 16, 8, 5, 6), (3, 1, 12, 20, 3, 9), (2, 2, 64, 64, 16, 16), (1, 1, 136, 40, 7, 4)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_delta_rule_kernels_over_steps(heads, kv_heads, dk, dv, ra, rg, out_dtype):
+    """prepare + scan + output over three steps of unequal portions, two sequences, state slots that held something
+    else before; against the plain recurrence over each whole sequence."""
+    from microllm_rocm_b200.kernels import recurrent
+    torch.manual_seed(dk + dv)
+    qk, vc = kv_heads * dk, heads * dv
+    lengths = [29, 6]
+    conv = [torch.randn(n, 2 * qk + vc, device=DEV) for n in lengths]                  # convolved and activated q | k | v
+    proj = [torch.randn(n, heads + ra + rg, device=DEV) for n in lengths]             # beta | a | g pre-activations
+    w_a2, w_g2 = torch.randn(heads * dk, ra, device=DEV) * 0.5, torch.randn(heads * dv, rg, device=DEV) * 0.5
+    dt_bias, a_log, norm_w = torch.randn(heads * dk, device=DEV), torch.randn(heads, device=DEV) - 1, 1 + 0.1 * torch.randn(dv, device=DEV)
+    state = torch.full((3, heads, dk, dv), 55.0, device=DEV)
+    cuts = [[(0, 11), (11, 12), (12, 29)], [(0, 2), (2, 4), (4, 6)]]
+    got = [torch.empty(n, vc, dtype=out_dtype, device=DEV) for n in lengths]
+    for step in range(3):
+        spans = [c[step] for c in cuts]
+        ctx, slots = step_of([b - a for a, b in spans], [a for a, _ in spans], [2, 1])
+        qkv = torch.cat([c[a:b] for c, (a, b) in zip(conv, spans)]).contiguous()
+        pr = torch.cat([p[a:b] for p, (a, b) in zip(proj, spans)]).contiguous()
+        T = qkv.shape[0]
+        qn, kn = torch.empty(T, qk, device=DEV), torch.empty(T, qk, device=DEV)
+        g, beta, o = torch.empty(T, heads * dk, device=DEV), torch.empty(T, heads, device=DEV), torch.empty(T, vc, device=DEV)
+        recurrent.delta_prepare(qkv, pr, 0, heads, w_a2, dt_bias, a_log, qn, kn, g, beta, heads, kv_heads, dk)
+        recurrent.delta_scan(qn, kn, g, beta, qkv[:, 2 * qk:], o, state, slots, ctx, heads, kv_heads, dk, dv)
+        out = torch.empty(T, vc, dtype=out_dtype, device=DEV)
+        recurrent.delta_output(o, norm_w, pr, heads + ra, w_g2, out, heads, dv, 1e-5)
+        assert int(ctx.error_flag.item()) == 0
+        at = 0
+        for i, (a, b) in enumerate(spans):
+            got[i][a:b] = out[at:at + b - a]
+            at += b - a
+    rep = heads // kv_heads
+    for i, n in enumerate(lengths):
+        c, p = conv[i].double().cpu(), proj[i].double().cpu()
+        unit = lambda x: x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-6)
+        q = (unit(c[:, :qk].view(n, kv_heads, dk)) * dk ** -0.5).repeat_interleave(rep, 1)
+        k = unit(c[:, qk:2 * qk].view(n, kv_heads, dk)).repeat_interleave(rep, 1)
+        v = c[:, 2 * qk:].view(n, heads, dv)
+        beta = torch.sigmoid(p[:, :heads])
+        pre = p[:, heads:heads + ra] @ w_a2.double().cpu().T + dt_bias.double().cpu()
+        g = torch.exp(-torch.exp(a_log.double().cpu())[None, :, None] * torch.nn.functional.softplus(pre).view(n, heads, dk))
+        o, _ = plain.delta_rule(q, k, v, g, beta)
+        gate = torch.sigmoid(p[:, heads + ra:] @ w_g2.double().cpu().T).view(n, heads, dv)
+        want = (plain.rms(o, 1e-5) * norm_w.double().cpu() * gate).reshape(n, vc)
+        assert torch.allclose(got[i].double().cpu(), want, atol=3e-5 if out_dtype == torch.float32 else 0.05), float((got[i].double().cpu() - want).abs().max())
+
+
+# ------------------------------------------------------------------------------------------- whole models
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["a", "b"])
+def test_every_layer_against_the_plain_residual_stream(folders, key, dtype):
+    from microllm_rocm_b200.engine.step import StepEntry
+    folder, raw, weights = folders[key]
+    tokens = random_tokens(41, raw["vocab"], 5)
+    want = []
+    plain.forward(raw, weights, tokens, want)
+    engine = engine_for(folder, dtype)
+    got = {}
+    engine.cache.add("x")
+    engine.step([StepEntry("x", tokens, [])], tensor_sink=lambda name, t: got.__setitem__(name, t.float().cpu().clone()))
+    engine.check_device_errors()
+    for i, ref in enumerate(want):
+        name = [n for n in got if n.startswith(f"run{i}.") and n.endswith(".residual")][0]
+        err = float((got[name].double() - ref).abs().max() / ref.abs().max())
+        assert err < (2e-5 if dtype == "float32" else 0.05), f"layer {i}: {err:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", sorted(CASES))
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions"])
+def test_one_request_at_a_time(folders, key, dtype, cut):
+    folder, raw, weights = folders[key]
+    reqs = requests_for(raw, LENGTHS[key])
+    steps = {"whole": steps_whole, "tail": steps_prefill_then_decode, "portions": steps_portions}[cut](reqs)
+    got = collect(engine_for(folder, dtype), steps)
+    compare(got, key, raw, weights, reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["a", "c"])
+def test_mixed_batches_over_a_tight_pool(folders, key, dtype):
+    """Up to four live requests, portions beside single tokens, some left out of a step; the pool holds just the peak and
+    there are four state slots for ten requests, so pages and slots go from one request to the next (a slot's old state
+    and convolution inputs must not leak into the request that takes it)."""
+    folder, raw, weights = folders[key]
+    reqs = requests_for(raw, [60, 33, 150, 90, 47, 128, 75, 20, 101, 64], seed=9)
+    steps, peak = steps_mixed(reqs, max_live=4, seed=3)
+    engine = engine_for(folder, dtype, max_tokens=peak, max_requests=4)
+    got = collect(engine, steps)
+    compare(got, key, raw, weights, reqs, dtype)
+    pool = engine.cache.groups["full"].pool
+    assert pool.total_allocations > pool.num_pages, "the pool was never tight enough to use a page again"
+    assert engine.cache.slots.total_allocations > 4, "no state slot was used again"
+
+
+def test_fp32_does_not_depend_on_cuts_batches_or_pages(folders):
+    folder, raw, weights = folders["a"]
+    reqs = requests_for(raw, [70, 133, 20, 45], seed=4)
+    whole = collect(engine_for(folder, "float32"), steps_whole(reqs))
+    portions = collect(engine_for(folder, "float32", page_size=8), steps_portions(reqs, sizes=(2, 9, 2, 30, 1, 5)))
+    steps, peak = steps_mixed(reqs, max_live=3, seed=1)
+    mixed = collect(engine_for(folder, "float32", max_tokens=peak), steps)
+    for k in whole:
+        assert torch.equal(whole[k], portions[k]) and torch.equal(whole[k], mixed[k]), f"{k} differs between schedules"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_far_keys_and_page_borders_decide_the_output(tmp_path_factory, dtype):
+    """Peaky softmax (the queries' norm weights scaled up): single keys, far back and at page borders, carry a
+    position's output, in a prompt of several hundred tokens and in the tokens decoded after it, with two page sizes."""
+    raw, weights = case("c", seed=11, sharp=6.0)
+    folder = write_folder(str(tmp_path_factory.mktemp("matidra_sharp")), raw, weights)
+    reqs = {"long": random_tokens(700, raw["vocab"], 21), "edge": random_tokens(16 * 9 + 1, raw["vocab"], 22)}
+    for page_size, steps in ((16, steps_prefill_then_decode(reqs, tail=40)), (32, steps_portions(reqs, sizes=(127, 2, 33, 1, 64, 300)))):
+        got = collect(engine_for(folder, dtype, max_tokens=1100, page_size=page_size), steps)
+        compare(got, "c-sharp", raw, weights, reqs, dtype)
+    # the softmax really is peaky: the largest weight of a late query is most of the sum
+    soft, _ = case("c", seed=11, sharp=1.0)
+    a = plain.forward(raw, weights, reqs["edge"][:60])
+    b = plain.forward(raw, case("c", seed=11, sharp=1.0)[1], reqs["edge"][:60])
+    assert float((a - b).abs().max() / a.abs().max()) > 10 * BF16_TOL
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_from_the_first_token(folders, dtype):
+    """One token per step from position 0 on, over many pages: every step reads and writes the state slots."""
+    folder, raw, weights = folders["d"]
+    reqs = {"d": random_tokens(150, raw["vocab"], 8)}
+    got = collect(engine_for(folder, dtype, page_size=8), steps_prefill_then_decode(reqs, tail=149))
+    compare(got, "d", raw, weights, reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_scheduler(folders, dtype):
+    from microllm_rocm_b200.engine.llm import LLM
+    from microllm_rocm_b200.sampling import GenerationConfig
+    folder, raw, weights = folders["a"]
+    prompts = [random_tokens(n, raw["vocab"], 50 + n) for n in (9, 40, 3)]
+    llm = LLM(folder, dtype=dtype, page_size=16, max_tokens=512)
+    outs = llm.generate(prompts, GenerationConfig(max_new_tokens=12, temperature=0.0))
+    for prompt, got in zip(prompts, outs):
+        assert len(got) == 12
+        seq = list(prompt)
+        for i, token in enumerate(got):
+            ref = plain.forward(raw, weights, seq)[-1]
+            if dtype == "float32":
+                assert token == int(ref.argmax()), f"token {i} differs from the plain greedy choice"
+            else:       # bf16 may leave the fp32 choice at a near tie: every pick must be a near maximum of the plain logits
+                assert float(ref.max() - ref[token]) <= 0.05 * float(ref.abs().max())
+            seq.append(token)
