@@ -217,11 +217,18 @@ class DecodeGraph:
     def capture(self) -> None:
         """Run the step once eagerly (plans launches, warms libraries), then record it.  The
         eager run really executes: callers `load()` the true state again afterwards."""
+        # Keys and values of the eager run land where the replay writes them again; fixed-size state (a recurrence,
+        # a convolution's last inputs) would be moved on twice.  The live requests' slots are put back after the run.
+        cache = self.engine.cache
+        slots = torch.tensor([cache.slot(q) for q in self.requests] + [cache.pad_slot], dtype=torch.long, device=self.engine.device)
+        kept = {name: storage.index_select(0, slots) for name, storage in cache.state_storage.items()}
         side = torch.cuda.Stream(device=self.engine.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             self._body()
         torch.cuda.current_stream().wait_stream(side)
+        for name, rows in kept.items():
+            cache.state_storage[name].index_copy_(0, slots, rows)
         torch.cuda.synchronize()
         from ..kernels.build import LaunchCounter
         before = LaunchCounter.own

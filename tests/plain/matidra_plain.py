@@ -109,7 +109,7 @@ def softmax_mixer(h, positions, w: Dict[str, torch.Tensor], p: str, m: dict, eps
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q, k = h @ w[p + "q"].T, h @ w[p + "k"].T
     v = k if values_are_keys else h @ w[p + "v"].T
-    if conv:
+    if conv and p + "q.conv" in w:
         q, k, v = (short_convolution(x, w[p + n + ".conv"]) for x, n in ((q, "q"), (k, "k"), (v, "v")))
     v = v.view(T, G, dv)
     q = rms(q.view(T, H, dk), eps) * w[p + "q.norm"]
@@ -131,9 +131,10 @@ def delta_mixer(h, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float):
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     silu = lambda x: x * torch.sigmoid(x)
-    q = silu(short_convolution(h @ w[p + "q"].T, w[p + "q.conv"])).view(T, G, dk)
-    k = silu(short_convolution(h @ w[p + "k"].T, w[p + "k.conv"])).view(T, G, dk)
-    v = silu(short_convolution(h @ w[p + "v"].T, w[p + "v.conv"])).view(T, H, dv)
+    conv = lambda x, n: short_convolution(x, w[p + n + ".conv"]) if p + n + ".conv" in w else x
+    q = silu(conv(h @ w[p + "q"].T, "q")).view(T, G, dk)
+    k = silu(conv(h @ w[p + "k"].T, "k")).view(T, G, dk)
+    v = silu(conv(h @ w[p + "v"].T, "v")).view(T, H, dv)
     unit = lambda x: x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-6)
     q, k = unit(q) * dk ** -0.5, unit(k)
     rep = H // G
