@@ -303,9 +303,14 @@ def step_timeline(session):
 # (its chosen experts plus the shared one).  Random weights, bf16.  Per design: one prompt step of --prefill-tokens
 # tokens, captured decode steps of --batch requests at context --prompt, and the kernels of one step of each kind
 # with their summed durations (for the comparison of like kernels).
+# The Matidra sizes (post-norm layers; softmax attention whose values are the keys, then layers of gated attention behind
+# short convolutions beside a gated delta rule) stand beside a Qwen2 of the same width, layers, feed-forward width and
+# vocabulary whose heads are those of Matidra's attention layer.
 DESIGN_SIZES = {
     "small": dict(gedalix="gedalix-small", layers=4),
     "16b-layers": dict(gedalix="gedalix-16b-layers", layers=4),
+    "matidra-small": dict(matidra="matidra-small", layers=4),
+    "matidra-3b-layers": dict(matidra="matidra-3b-layers", layers=4),
 }
 
 
@@ -317,6 +322,16 @@ def _equal_dense(raw, layers):
     return Qwen2Config.from_dict(dict(vocab_size=raw["vocab"], hidden_size=raw["width"], num_hidden_layers=layers,
                                       num_attention_heads=m["heads"], num_key_value_heads=max(1, m["heads"] // 8), head_dim=m["dim"],
                                       intermediate_size=inter, max_position_embeddings=raw["max_positions"], rope_theta=1e6,
+                                      rms_norm_eps=1e-6, tie_word_embeddings=False))
+
+
+def _equal_dense_matidra(raw, layers, max_positions):
+    from microllm_rocm_b200.config import Qwen2Config
+    first = next(l for l in raw["layers"] if l["type"] == "attention")
+    m = first["mixer"]
+    return Qwen2Config.from_dict(dict(vocab_size=raw["vocab"], hidden_size=raw["width"], num_hidden_layers=layers,
+                                      num_attention_heads=m["heads"], num_key_value_heads=m["kv_heads"], head_dim=m["dim"],
+                                      intermediate_size=first["mlp"]["ff"], max_position_embeddings=max_positions, rope_theta=1e6,
                                       rms_norm_eps=1e-6, tie_word_embeddings=False))
 
 
@@ -336,7 +351,7 @@ def _kernel_rows(step_fn, repeats=3):
         row[0] += 1
         row[1] += duration
         row[2] += exposed
-    return [(n, c, round(d, 1), round(e, 1)) for n, (c, d, e) in sorted(rows.items(), key=lambda kv: -kv[1][2])][:14]
+    return [(n, c, round(d, 1), round(e, 1)) for n, (c, d, e) in sorted(rows.items(), key=lambda kv: -kv[1][2])][:20]
 
 
 def run_designs(args):
@@ -354,11 +369,18 @@ def run_designs(args):
     gen = torch.Generator().manual_seed(0)
     for name in names:
         size = DESIGN_SIZES[name]
-        raw = copy.deepcopy(GEDALIX_PRESETS[size["gedalix"]])
         layers = args.layers or size["layers"]
-        raw["layers"] = raw["layers"][:layers]
-        raw["max_positions"] = max(raw["max_positions"], args.prompt + 512)
-        designs = {"gedalix": GedalixConfig.from_dict(raw), "qwen2": _equal_dense(raw, layers)}
+        if "matidra" in size:
+            from microllm_rocm_b200.config.matidra import PRESETS as MATIDRA_PRESETS, MatidraConfig
+            raw = copy.deepcopy(MATIDRA_PRESETS[size["matidra"]])
+            raw["layers"] = raw["layers"][:layers]
+            raw["max_positions"] = args.prompt + 512
+            designs = {"matidra": MatidraConfig.from_dict(raw), "qwen2": _equal_dense_matidra(raw, layers, args.prompt + 512)}
+        else:
+            raw = copy.deepcopy(GEDALIX_PRESETS[size["gedalix"]])
+            raw["layers"] = raw["layers"][:layers]
+            raw["max_positions"] = max(raw["max_positions"], args.prompt + 512)
+            designs = {"gedalix": GedalixConfig.from_dict(raw), "qwen2": _equal_dense(raw, layers)}
         result = {}
         for design, cfg in designs.items():
             page = 64

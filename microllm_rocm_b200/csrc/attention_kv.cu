@@ -46,6 +46,7 @@ struct PrepareParams {
     void* q_out;               // [T, H * DK]
     void* pages;
     int T, H, G, DK, DV;
+    int PK, PV;                // widths of a stored query / key row and of a stored value row (>= DK, DV; the rest is zero)
     int* error_flag;
 };
 
@@ -63,6 +64,7 @@ __global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p)
     const bool is_q = which < p.H, is_k = !is_q && which < p.H + p.G;
     const int head = is_q ? which : (is_k ? which - p.H : which - p.H - p.G);
     const int D = (is_q || is_k) ? p.DK : p.DV;
+    const int P = (is_q || is_k) ? p.PK : p.PV;       // stored width
     if (!is_q) {
         if (!p.pages) return;
         const int seq = p.token_seq[t];
@@ -72,9 +74,9 @@ __global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p)
             if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 1);
             return;
         }
-        const size_t page_stride = (size_t)p.G * p.page_size * (p.DK + p.DV);
-        const size_t within = is_k ? ((size_t)head * p.page_size + pos % p.page_size) * p.DK
-                                   : (size_t)p.G * p.page_size * p.DK + ((size_t)head * p.page_size + pos % p.page_size) * p.DV;
+        const size_t page_stride = (size_t)p.G * p.page_size * (p.PK + p.PV);
+        const size_t within = is_k ? ((size_t)head * p.page_size + pos % p.page_size) * p.PK
+                                   : (size_t)p.G * p.page_size * p.PK + ((size_t)head * p.page_size + pos % p.page_size) * p.PV;
         page_row = (KVT*)p.pages + (size_t)page * page_stride + within;
     }
     const Columns& src = is_q ? p.q : (is_k ? p.k : p.v);
@@ -116,12 +118,12 @@ __global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p)
         }
     }
     if (is_q) {
-        OutT* out = (OutT*)p.q_out + ((size_t)t * p.H + head) * p.DK;
+        OutT* out = (OutT*)p.q_out + ((size_t)t * p.H + head) * P;
 #pragma unroll
-        for (int i = 0; i < PER_LANE; ++i) { const int c = lane + 32 * i; if (c < D) out[c] = from_f32<OutT>(x[i]); }
+        for (int i = 0; i < PER_LANE; ++i) { const int c = lane + 32 * i; if (c < P) out[c] = from_f32<OutT>(c < D ? x[i] : 0.0f); }
     } else {
 #pragma unroll
-        for (int i = 0; i < PER_LANE; ++i) { const int c = lane + 32 * i; if (c < D) page_row[c] = from_f32<KVT>(x[i]); }
+        for (int i = 0; i < PER_LANE; ++i) { const int c = lane + 32 * i; if (c < P) page_row[c] = from_f32<KVT>(c < D ? x[i] : 0.0f); }
     }
 }
 
@@ -224,19 +226,56 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kv_kernel(AttnPara
     }
 }
 
+// out[t, h * DV + c] = o[t, h * PV + c] * sigmoid(gate[t, gate_col + h * DV + c]): the heads' outputs taken out of rows
+// that are wider than a value (an attention kernel that ran on padded heads) and gated.  gate.base null: no gate.
+struct GateParams {
+    const void* o; void* out; Columns gate; int gate_col; int T, H, DV, PV;
+};
+
+template <typename T>
+__global__ void gate_heads_kernel(GateParams p) {
+    pdl_prologue();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long n = (long long)p.T * p.H * p.DV;
+    if (i >= n) return;
+    const int c = (int)(i % p.DV), h = (int)((i / p.DV) % p.H);
+    const long long t = i / ((long long)p.DV * p.H);
+    float o = to_f32(((const T*)p.o)[(t * p.H + h) * p.PV + c]);
+    if (p.gate.base) {
+        const float g = p.gate.at(t, p.gate_col + h * p.DV + c);
+        o *= g >= 0.0f ? 1.0f / (1.0f + expf(-g)) : expf(g) / (1.0f + expf(g));
+    }
+    ((T*)p.out)[i] = from_f32<T>(o);
+}
+
 }  // namespace
+
+MLB_EXPORT int mlb_gate_heads(const void* o, void* out, int dtype, const float* gate, long long gate_ld, int gate_partials,
+                              long long gate_partial_stride, int gate_col, int T, int H, int DV, int stored_v, cudaStream_t stream) {
+    if (T < 0 || H <= 0 || DV <= 0 || stored_v < DV || !o || !out) return fail(MLB_INVALID_ARGUMENT, "gate_heads: bad operands");
+    if (T == 0) return MLB_OK;
+    GateParams p{o, out, Columns{gate, gate_ld, gate_partials < 1 ? 1 : gate_partials, gate_partial_stride}, gate_col, T, H, DV, stored_v};
+    const long long n = (long long)T * H * DV;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == MLB_BF16) launch_kernel(gate_heads_kernel<__nv_bfloat16>, blocks, 256, 0, stream, p);
+    else if (dtype == MLB_F32) launch_kernel(gate_heads_kernel<float>, blocks, 256, 0, stream, p);
+    else return fail(MLB_INVALID_ARGUMENT, "gate_heads: unsupported dtype %d", dtype);
+    return check_launch("gate_heads");
+}
 
 MLB_EXPORT int mlb_qk_prepare(const float* src, long long ld, int n_partials, long long partial_stride, int q_col, int k_col,
                               int v_col, const float* kv_src, long long kv_ld, int kv_partials, long long kv_partial_stride,
                               const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_dims,
                               float magnitude, float temp_coef, int temp_every, const int* positions, const int* token_seq,
                               const int* block_table, int max_blocks, int num_pages, int page_size, void* q_out, int q_dtype,
-                              void* pages, int kv_dtype, int T, int H, int G, int DK, int DV, int* error_flag,
-                              cudaStream_t stream) {
+                              void* pages, int kv_dtype, int T, int H, int G, int DK, int DV, int stored_k, int stored_v,
+                              int* error_flag, cudaStream_t stream) {
     // `src` holds q (and k, v when kv_src is null); `kv_src`, when given, holds k and v (a projection that went through
     // another kernel first: the raw values of "values are the projected keys" come from the same place as k)
     if (T < 0 || H <= 0 || G <= 0 || H % G || DK <= 0 || DV <= 0 || DK > MAX_D || DV > MAX_D)
         return fail(MLB_UNSUPPORTED_SIZE, "qk_prepare: heads %d/%d, widths %d/%d (at most %d)", H, G, DK, DV, MAX_D);
+    if (stored_k < DK || stored_v < DV || stored_k > MAX_D || stored_v > MAX_D)
+        return fail(MLB_INVALID_ARGUMENT, "qk_prepare: stored widths %d/%d for %d/%d (at most %d)", stored_k, stored_v, DK, DV, MAX_D);
     if (rot_dims < 0 || rot_dims % 2 || rot_dims > DK) return fail(MLB_INVALID_ARGUMENT, "qk_prepare: rot_dims %d of %d", rot_dims, DK);
     if (pages && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !block_table))
         return fail(MLB_INVALID_ARGUMENT, "qk_prepare: bad cache geometry");
@@ -248,7 +287,7 @@ MLB_EXPORT int mlb_qk_prepare(const float* src, long long ld, int n_partials, lo
     p.q_norm = q_norm; p.k_norm = k_norm; p.eps = eps; p.freq = freq; p.rot_dims = rot_dims; p.magnitude = magnitude;
     p.temp_coef = temp_coef; p.temp_every = temp_every; p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
     p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.q_out = q_out; p.pages = pages;
-    p.T = T; p.H = H; p.G = G; p.DK = DK; p.DV = DV; p.error_flag = error_flag;
+    p.T = T; p.H = H; p.G = G; p.DK = DK; p.DV = DV; p.PK = stored_k; p.PV = stored_v; p.error_flag = error_flag;
     const long long items = (long long)T * (H + 2 * G);
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
     const int kvd = pages ? kv_dtype : q_dtype;

@@ -21,7 +21,8 @@ MAX_WIDTH = 256
 ops.register_signatures("attention_kv.cu", {
     "mlb_qk_prepare": [c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_longlong,
                        c_void_p, c_void_p, c_float, c_void_p, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p,
-                       c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                       c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "mlb_gate_heads": [c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "mlb_paged_attention_kv": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_longlong, c_int, c_longlong, c_int,
                                c_void_p, c_void_p],
@@ -55,9 +56,10 @@ def qk_prepare(src: torch.Tensor, q_col: int, k_col: int, v_col: int, *, kv_src:
                q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float, freq: Optional[torch.Tensor],
                rot_dims: int, magnitude: float, q_temp, positions: torch.Tensor, token_seq: torch.Tensor,
                block_table: Optional[torch.Tensor], pages: Optional[torch.Tensor], page_size: int, q_out: torch.Tensor,
-               heads: int, kv_heads: int, dk: int, dv: int, error_flag: Optional[torch.Tensor]) -> None:
+               heads: int, kv_heads: int, dk: int, dv: int, error_flag: Optional[torch.Tensor], stored: Optional[int] = None) -> None:
     """q, k, v are column blocks (first columns q_col, k_col, v_col) of `src`; k and v of `kv_src` when that is given.
-    `q_temp`: None or (coef, every).  `pages` None: only the queries are made."""
+    `q_temp`: None or (coef, every).  `pages` None: only the queries are made.  `stored`: the width every query, key and
+    value row is stored with (zeros behind its own elements), for an attention kernel that wants one width for all."""
     _, ld, n, stride = _columns(src, "src")
     kv_ptr, kv_ld, kv_n, kv_stride = None, 0, 0, 0
     if kv_src is not None:
@@ -65,12 +67,13 @@ def qk_prepare(src: torch.Tensor, q_col: int, k_col: int, v_col: int, *, kv_src:
         kv_ptr = kv_src.data_ptr()
     T = src.shape[-2]
     ops._need(q_out, "q_out", dims=2)
-    if q_out.shape != (T, heads * dk):
-        raise KernelError("qk_prepare: q_out must be [T, heads * dk]")
+    sk, sv = (stored, stored) if stored else (dk, dv)
+    if q_out.shape != (T, heads * sk):
+        raise KernelError("qk_prepare: q_out must be [T, heads * (stored) key width]")
     num_pages = max_blocks = 0
     if pages is not None:
         ops._need(block_table, "block_table", torch.int32, 2)
-        if pages.numel() % pages.shape[0] or pages.numel() // pages.shape[0] != page_elements(kv_heads, page_size, dk, dv):
+        if pages.numel() % pages.shape[0] or pages.numel() // pages.shape[0] != page_elements(kv_heads, page_size, sk, sv):
             raise KernelError(f"qk_prepare: pages {tuple(pages.shape)} do not match the head geometry")
         num_pages, max_blocks = pages.shape[0], block_table.shape[1]
     coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
@@ -79,8 +82,24 @@ def qk_prepare(src: torch.Tensor, q_col: int, k_col: int, v_col: int, *, kv_src:
         src.data_ptr(), ld, n, stride, q_col, k_col, v_col, kv_ptr, kv_ld, kv_n, kv_stride, ops._ptr(q_norm), ops._ptr(k_norm),
         float(eps), ops._ptr(freq) if rot_dims else None, int(rot_dims), float(magnitude), coef, every, positions.data_ptr(),
         token_seq.data_ptr(), ops._ptr(block_table), max_blocks, num_pages, page_size, q_out.data_ptr(), ops.dtype_tag(q_out),
-        ops._ptr(pages), ops.dtype_tag(pages) if pages is not None else ops.F32, T, heads, kv_heads, dk, dv,
+        ops._ptr(pages), ops.dtype_tag(pages) if pages is not None else ops.F32, T, heads, kv_heads, dk, dv, sk, sv,
         ops._ptr(error_flag), ops._stream()))
+
+
+def gate_heads(o: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], gate_col: int, heads: int, dv: int, stored: int) -> None:
+    """out[T, heads * dv] = the first dv elements of each head of o[T, heads * stored], times sigmoid(gate columns from
+    gate_col of fp32 rows or partial results) when a gate is given."""
+    ops._need(o, "o", dims=2); ops._need(out, "out", dims=2)
+    T = o.shape[0]
+    if o.shape[1] != heads * stored or out.shape != (T, heads * dv) or o.dtype != out.dtype:
+        raise KernelError("gate_heads: shapes do not agree")
+    g_ptr, g_ld, g_n, g_stride = None, 0, 1, 0
+    if gate is not None:
+        _, g_ld, g_n, g_stride = _columns(gate, "gate")
+        g_ptr = gate.data_ptr()
+    L = ops.lib("attention_kv.cu")
+    build.check(L, L.mlb_gate_heads(o.data_ptr(), out.data_ptr(), ops.dtype_tag(o), g_ptr, g_ld, g_n, g_stride, int(gate_col), T, heads,
+                                    dv, stored, ops._stream()))
 
 
 def paged_attention_kv(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,

@@ -22,12 +22,14 @@ ops.register_signatures("short_conv.cu", {
                              c_int, c_void_p],
 })
 ops.register_signatures("delta_rule.cu", {
-    "mlb_delta_prepare": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
+    "mlb_delta_prepare": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_longlong,
+                          c_int, c_longlong, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "mlb_take_columns": [c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "mlb_delta_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
-    "mlb_delta_output": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-                         c_int, c_int, c_float, c_void_p],
+    "mlb_delta_output": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int,
+                         c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
 })
 
 
@@ -65,24 +67,49 @@ def short_conv(u: torch.Tensor, col0: int, weight: torch.Tensor, state: Optional
                                               ctx.seq_starts.data_ptr(), ctx.num_seqs, C, taps, ops._stream()))
 
 
-def delta_prepare(qkv: torch.Tensor, proj: torch.Tensor, beta_col: int, a_col: int, w2: torch.Tensor, dt_bias: torch.Tensor,
+def _pre(pre: Optional[torch.Tensor], T: int, width: int, what: str):
+    if pre is None:
+        return None, 0, 1, 0
+    _, ld, n, stride = _columns(pre, what)
+    if pre.shape[-2] != T or ld != width:
+        raise KernelError(f"{what} must be [T, {width}] or its partial results")
+    return pre.data_ptr(), ld, n, stride
+
+
+def take_columns(src: torch.Tensor, col0: int, out: torch.Tensor) -> None:
+    """out[t, c] = src[t, col0 + c], `src` fp32 rows or their [S, T, N] partial results (summed), in out's dtype."""
+    _, ld, n, stride = _columns(src, "src")
+    ops._need(out, "out", dims=2)
+    if out.shape[0] != src.shape[-2] or col0 < 0 or col0 + out.shape[1] > ld:
+        raise KernelError("take_columns: shapes do not agree")
+    L = ops.lib("delta_rule.cu")
+    build.check(L, L.mlb_take_columns(src.data_ptr(), ld, n, stride, col0, out.shape[1], out.shape[0], out.data_ptr(),
+                                      ops.dtype_tag(out), ops._stream()))
+
+
+def delta_prepare(qkv: torch.Tensor, proj: torch.Tensor, beta_col: int, a_col: int, w2: Optional[torch.Tensor], dt_bias: torch.Tensor,
                   a_log: torch.Tensor, qn: torch.Tensor, kn: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, heads: int,
-                  kv_heads: int, dk: int) -> None:
+                  kv_heads: int, dk: int, pre: Optional[torch.Tensor] = None) -> None:
     """Unit-vector q (times dk^-1/2) and k per kv head from the first 2 * kv_heads * dk columns of `qkv`; per head
-    beta = sigmoid(proj[:, beta_col + h]) and the decay g = exp(-exp(a_log[h]) * softplus(w2 proj[:, a_col:] + dt_bias))."""
+    beta = sigmoid(proj[:, beta_col + h]) and the decay g = exp(-exp(a_log[h]) * softplus(w2 proj[:, a_col:] + dt_bias)).
+    `pre` [T, heads * dk] (or partial results): w2 proj[:, a_col:] already made by a product; else it is made here."""
     ops._need(qkv, "qkv", torch.float32, 2)
     _, ld, n, stride = _columns(proj, "proj")
     T = qkv.shape[0]
-    for name, t, shape in (("w2", w2, (heads * dk, w2.shape[-1])), ("dt_bias", dt_bias, (heads * dk,)), ("a_log", a_log, (heads,)),
+    if (w2 is None) == (pre is None):
+        raise KernelError("delta_prepare: either the second projection's weight or its result")
+    rank = w2.shape[-1] if w2 is not None else 1
+    pre_args = _pre(pre, T, heads * dk, "delta_prepare pre")
+    for name, t, shape in ((("w2", w2, (heads * dk, rank)),) if w2 is not None else ()) + (("dt_bias", dt_bias, (heads * dk,)), ("a_log", a_log, (heads,)),
                            ("qn", qn, (T, kv_heads * dk)), ("kn", kn, (T, kv_heads * dk)), ("g", g, (T, heads * dk)),
                            ("beta", beta, (T, heads))):
         ops._need(t, name, torch.float32)
         if tuple(t.shape) != shape:
             raise KernelError(f"delta_prepare: {name} must be {shape}, got {tuple(t.shape)}")
     L = ops.lib("delta_rule.cu")
-    build.check(L, L.mlb_delta_prepare(qkv.data_ptr(), qkv.shape[1], proj.data_ptr(), ld, n, stride, beta_col, a_col, w2.data_ptr(),
-                                       dt_bias.data_ptr(), a_log.data_ptr(), qn.data_ptr(), kn.data_ptr(), g.data_ptr(),
-                                       beta.data_ptr(), T, heads, kv_heads, dk, w2.shape[1], ops._stream()))
+    build.check(L, L.mlb_delta_prepare(qkv.data_ptr(), qkv.shape[1], proj.data_ptr(), ld, n, stride, beta_col, a_col, ops._ptr(w2),
+                                       *pre_args, dt_bias.data_ptr(), a_log.data_ptr(), qn.data_ptr(), kn.data_ptr(), g.data_ptr(),
+                                       beta.data_ptr(), T, heads, kv_heads, dk, rank, ops._stream()))
 
 
 def delta_scan(qn: torch.Tensor, kn: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, v: torch.Tensor, o: torch.Tensor,
@@ -99,15 +126,21 @@ def delta_scan(qn: torch.Tensor, kn: torch.Tensor, g: torch.Tensor, beta: torch.
                                     ops._stream()))
 
 
-def delta_output(o: torch.Tensor, weight: torch.Tensor, proj: torch.Tensor, g_col: int, w2: torch.Tensor, out: torch.Tensor,
-                 heads: int, dv: int, eps: float) -> None:
-    """out = o / rms(o) per head * weight * sigmoid(w2 proj[:, g_col:g_col + rank]) in out's dtype."""
-    ops._need(o, "o", torch.float32, 2); ops._need(weight, "weight", torch.float32, 1); ops._need(w2, "w2", torch.float32, 2)
+def delta_output(o: torch.Tensor, weight: torch.Tensor, proj: torch.Tensor, g_col: int, w2: Optional[torch.Tensor], out: torch.Tensor,
+                 heads: int, dv: int, eps: float, pre: Optional[torch.Tensor] = None) -> None:
+    """out = o / rms(o) per head * weight * sigmoid(w2 proj[:, g_col:g_col + rank]) in out's dtype; `pre` as in delta_prepare."""
+    ops._need(o, "o", torch.float32, 2); ops._need(weight, "weight", torch.float32, 1)
     ops._need(out, "out", dims=2)
     _, ld, n, stride = _columns(proj, "proj")
     T = o.shape[0]
-    if o.shape != (T, heads * dv) or out.shape != o.shape or weight.shape[0] != dv or w2.shape[0] != heads * dv:
+    if (w2 is None) == (pre is None):
+        raise KernelError("delta_output: either the second projection's weight or its result")
+    if w2 is not None:
+        ops._need(w2, "w2", torch.float32, 2)
+    rank = w2.shape[1] if w2 is not None else 1
+    pre_args = _pre(pre, T, heads * dv, "delta_output pre")
+    if o.shape != (T, heads * dv) or out.shape != o.shape or weight.shape[0] != dv or (w2 is not None and w2.shape[0] != heads * dv):
         raise KernelError("delta_output: shapes do not agree")
     L = ops.lib("delta_rule.cu")
-    build.check(L, L.mlb_delta_output(o.data_ptr(), weight.data_ptr(), proj.data_ptr(), ld, n, stride, g_col, w2.data_ptr(),
-                                      out.data_ptr(), ops.dtype_tag(out), T, heads, dv, w2.shape[1], float(eps), ops._stream()))
+    build.check(L, L.mlb_delta_output(o.data_ptr(), weight.data_ptr(), proj.data_ptr(), ld, n, stride, g_col, ops._ptr(w2), *pre_args,
+                                      out.data_ptr(), ops.dtype_tag(out), T, heads, dv, rank, float(eps), ops._stream()))

@@ -24,6 +24,7 @@ from .base import Mixer, PagedKVNeed, PagedKVView, PositionEncoding, Runtime, St
 
 
 ROPE_TABLE_MIN_TOKENS = 64          # from here on a step-wide table of sines and cosines pays
+SHARED_KERNEL_WIDTHS = (32, 64, 128)   # head sizes at which the tensor-core attention kernels of one width are built and tested
 
 
 @register_mixer("attention")
@@ -208,12 +209,20 @@ class NormedAttention(Mixer):
         self.v_cols = self.nkv * self.dv if self.values == "projected" else 0
         self.g_cols = self.nh * self.dv if self.has_gate else 0
         self.conv_cols = self.q_cols + self.k_cols + self.v_cols
+        # bf16: the attention itself runs on the tensor-core kernels of equal key and value widths; unequal widths are
+        # stored with zeros up to one width that those kernels take (the plain kernel with the true widths otherwise,
+        # and always in fp32, where every kernel is a plain one)
+        self.stored = None
+        if not rt.is_fp32:
+            wide = -(-max(self.dk, self.dv) // 32) * 32
+            if wide in SHARED_KERNEL_WIDTHS:
+                self.stored = wide
         self.w_in = self.w_o = self.q_norm_w = self.k_norm_w = self.w_conv = None
 
     # --- declarations -----------------------------------------------------------------
     def cache_need(self):
         from .base import CompositeNeed, FixedStateNeed
-        kv = PagedKVNeed(self.nkv, self.dk, self.window, value_dim=self.dv)
+        kv = PagedKVNeed(self.nkv, self.dk, self.window, value_dim=self.dv) if self.stored is None else PagedKVNeed(self.nkv, self.stored, self.window)
         if self.taps <= 1:
             return kv
         return CompositeNeed((("kv", kv), ("conv", FixedStateNeed((self.taps - 1, self.conv_cols), torch.float32))))
@@ -258,8 +267,8 @@ class NormedAttention(Mixer):
         if self.rt.is_fp32:
             return own
         own += gemm_bf16.sources(engine_only=True)
-        if self.dk == self.dv:
-            own += attention_kernels.mma_sources(self.dk) + attention_kernels.tc_sources(self.dk)
+        if self.stored is not None:
+            own += attention_kernels.mma_sources(self.stored) + attention_kernels.tc_sources(self.stored)
         return own
 
     def bind(self, tensors):
@@ -289,8 +298,8 @@ class NormedAttention(Mixer):
         return [self.w_in, self.w_o, self.q_norm_w, self.k_norm_w, self.w_conv]
 
     def _shared_kernels(self, page_size: int) -> bool:
-        """Whether the attention itself can run on the kernels of equal key and value widths."""
-        return (self.dk == self.dv and not self.rt.is_fp32 and attention_kernels.mma_supported(self.dk, page_size))
+        """Whether the attention itself runs on the kernels of equal key and value widths."""
+        return self.stored is not None and attention_kernels.mma_supported(self.stored, page_size)
 
     def plan_stale(self, ctx: StepContext, max_seq_len: int) -> bool:
         from ..kernels.device import sm_count
@@ -315,19 +324,28 @@ class NormedAttention(Mixer):
             state = cache["conv"]
             src = ctx.buffer("normed_attention.conv", (T, self.conv_cols), torch.float32)
             recurrent.short_conv(proj, 0, self.w_conv, state.storage, state.slots, ctx, src, silu=False, update_state=state.writable)
-        q = ctx.buffer("normed_attention.q", (T, self.q_cols), dt)
+        sk = self.stored or self.dk
+        sv = self.stored or self.dv
+        q = ctx.buffer("normed_attention.q", (T, self.nh * sk), dt)
         attention_kv.qk_prepare(src, q_col, k_col, v_col, q_norm=self.q_norm_w, k_norm=self.k_norm_w, eps=self.eps, freq=self.freq,
                                 rot_dims=self.rot_dims, magnitude=self.magnitude, q_temp=self.q_temp, positions=ctx.positions,
                                 token_seq=ctx.token_seq, block_table=kv_view.block_table,
                                 pages=kv_view.pages if kv_view.writable else None, page_size=kv_view.page_size, q_out=q,
-                                heads=self.nh, kv_heads=self.nkv, dk=self.dk, dv=self.dv, error_flag=flag)
+                                heads=self.nh, kv_heads=self.nkv, dk=self.dk, dv=self.dv, error_flag=flag, stored=self.stored)
         o = ctx.buffer("normed_attention.o", (T, self.nh * self.dv), dt)
-        if self._shared_kernels(kv_view.page_size) and not self.has_gate:
-            attention_kernels.paged_attention(q, kv_view.pages, o, ctx, kv_view.block_table, self.nh, self.nkv, self.dk, self.scale,
+        gate = proj if self.has_gate else None
+        if self._shared_kernels(kv_view.page_size):
+            wide = o if (sv == self.dv and gate is None) else ctx.buffer("normed_attention.o_stored", (T, self.nh * sv), dt)
+            attention_kernels.paged_attention(q, kv_view.pages, wide, ctx, kv_view.block_table, self.nh, self.nkv, sk, self.scale,
                                               self.window, beside_mma_products=gemm_bf16.gemv_preferred(x, self.w_o))
+            if wide is not o:
+                attention_kv.gate_heads(wide, o, gate, self.conv_cols, self.nh, self.dv, sv)
+        elif self.stored is not None:            # a page size the tensor-core kernels do not take: the plain kernel of one width
+            wide = ctx.buffer("normed_attention.o_stored", (T, self.nh * sv), dt)
+            attention_kernels.paged_attention(q, kv_view.pages, wide, ctx, kv_view.block_table, self.nh, self.nkv, sk, self.scale, self.window)
+            attention_kv.gate_heads(wide, o, gate, self.conv_cols, self.nh, self.dv, sv)
         else:
             attention_kv.paged_attention_kv(q, kv_view.pages, o, ctx.positions, ctx.token_seq, kv_view.block_table, kv_view.page_size,
-                                            self.nh, self.nkv, self.dk, self.dv, self.scale, self.window,
-                                            proj if self.has_gate else None, self.conv_cols, flag)
+                                            self.nh, self.nkv, self.dk, self.dv, self.scale, self.window, gate, self.conv_cols, flag)
         return linear(o, self.w_o, None, torch.float32, partials_ok=True, error_flag=flag,
                       alloc=lambda shape, dtype: ctx.buffer("normed_attention.out", shape, dtype))

@@ -54,6 +54,9 @@ class GatedDeltaRule(Mixer):
         self.a_col = self.beta_col + self.nh
         self.g_col = self.a_col + self.a_rank
         self.in_rows = self.g_col + self.g_rank
+        # the second steps of the two narrow projections run as products when their inner widths suit the product
+        # kernels (multiples of 8), else inside the kernels that need their results
+        self.a_product, self.g_product = self.a_rank % 8 == 0, self.g_rank % 8 == 0
         self.w_in = self.w_o = self.w_conv = self.w_a2 = self.w_g2 = self.a_log = self.dt_bias = self.norm_w = None
 
     # --- declarations -----------------------------------------------------------------
@@ -72,8 +75,8 @@ class GatedDeltaRule(Mixer):
         n, W = self.names, self.hidden
         specs = {n["q"]: WeightSpec((self.q_cols, W)), n["k"]: WeightSpec((self.k_cols, W)), n["v"]: WeightSpec((self.v_cols, W)),
                  n["beta"]: WeightSpec((self.nh, W)), n["a1"]: WeightSpec((self.a_rank, W)), n["g1"]: WeightSpec((self.g_rank, W)),
-                 n["a2"]: WeightSpec((self.nh * self.dk, self.a_rank), role="vector", init=("normal", 0.1)),
-                 n["g2"]: WeightSpec((self.nh * self.dv, self.g_rank), role="vector", init=("normal", 0.1)),
+                 n["a2"]: WeightSpec((self.nh * self.dk, self.a_rank), role="matrix" if self.a_product else "vector", init=("normal", 0.1)),
+                 n["g2"]: WeightSpec((self.nh * self.dv, self.g_rank), role="matrix" if self.g_product else "vector", init=("normal", 0.1)),
                  n["a_log"]: WeightSpec((self.nh,), role="vector", init=("normal", 0.5)),
                  n["dt_bias"]: WeightSpec((self.nh * self.dk,), role="vector", init=("normal", 0.5)),
                  n["norm"]: WeightSpec((self.dv,), role="vector", init=("one_plus_normal", 0.1)),
@@ -132,12 +135,24 @@ class GatedDeltaRule(Mixer):
         kn = ctx.buffer("delta_rule.kn", (T, self.k_cols), f32)
         g = ctx.buffer("delta_rule.g", (T, self.nh * self.dk), f32)
         beta = ctx.buffer("delta_rule.beta", (T, self.nh), f32)
-        recurrent.delta_prepare(qkv, proj, self.beta_col, self.a_col, self.w_a2, self.dt_bias, self.a_log, qn, kn, g, beta,
-                                self.nh, self.nkv, self.dk)
+        a_pre = g_pre = None
+        if self.a_product:
+            narrow = ctx.buffer("delta_rule.a", (T, self.a_rank), self.rt.dtype)
+            recurrent.take_columns(proj, self.a_col, narrow)
+            a_pre = linear(narrow, self.w_a2, None, f32, partials_ok=True, error_flag=flag,
+                           alloc=lambda shape, dtype: ctx.buffer("delta_rule.a_pre", shape, dtype))
+        if self.g_product:
+            narrow = ctx.buffer("delta_rule.g_in", (T, self.g_rank), self.rt.dtype)
+            recurrent.take_columns(proj, self.g_col, narrow)
+            g_pre = linear(narrow, self.w_g2, None, f32, partials_ok=True, error_flag=flag,
+                           alloc=lambda shape, dtype: ctx.buffer("delta_rule.g_pre", shape, dtype))
+        recurrent.delta_prepare(qkv, proj, self.beta_col, self.a_col, None if self.a_product else self.w_a2, self.dt_bias, self.a_log,
+                                qn, kn, g, beta, self.nh, self.nkv, self.dk, pre=a_pre)
         o = ctx.buffer("delta_rule.o", (T, self.v_cols), f32)
         recurrent.delta_scan(qn, kn, g, beta, qkv[:, self.q_cols + self.k_cols:], o, state.storage, state.slots, ctx, self.nh,
                              self.nkv, self.dk, self.dv)
         gated = ctx.buffer("delta_rule.gated", (T, self.v_cols), self.rt.dtype)
-        recurrent.delta_output(o, self.norm_w, proj, self.g_col, self.w_g2, gated, self.nh, self.dv, self.eps)
+        recurrent.delta_output(o, self.norm_w, proj, self.g_col, None if self.g_product else self.w_g2, gated, self.nh, self.dv, self.eps,
+                               pre=g_pre)
         return linear(gated, self.w_o, None, f32, partials_ok=True, error_flag=flag,
                       alloc=lambda shape, dtype: ctx.buffer("delta_rule.out", shape, dtype))
