@@ -110,22 +110,36 @@ struct ScanParams {
     const int* slots; int num_slots;
     const int* seq_starts; const int* seq_pos0;
     int A, H, G, DK, DV;
+    int vec;                                 // 1: every staged row starts on 16 bytes and is a multiple of four floats long
     int* error_flag;
 };
 
 constexpr int SCAN_LANES = 8, SCAN_THREADS = 128, SCAN_COLS = SCAN_THREADS / SCAN_LANES;
 
-// ROWS: rows of a column that one lane keeps (DK <= 8 * ROWS).  CHUNK: tokens whose q, k, g, v and beta are staged in
-// shared memory at a time; the next chunk's values are fetched into registers before the present chunk is computed
-// and stored behind it, so the recurrence never waits for global memory inside a chunk.
+__device__ __forceinline__ void copy_async_f32(float* to_shared, const float* from, bool real) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(to_shared);
+    const int bytes = real ? 4 : 0;                            // 0: the four bytes are filled with zeros
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(from), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void copy_async_f32x4(float* to_shared, const float* from, bool real) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(to_shared);
+    const int bytes = real ? 16 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(from), "r"(bytes) : "memory");
+}
+
+// ROWS: rows of a column that one lane keeps (DK <= 8 * ROWS, ROWS a multiple of 4): lane `part` of a column owns rows
+// 32 j + 4 part + (0..3), so that the eight lanes of a column read 128 consecutive bytes of q, k and g at a time.
+// CHUNK: tokens whose q, k, g, v and beta are staged in shared memory at a time; the next chunk is copied there
+// asynchronously (cp.async, zero fill for padding) while the present one is computed, so the recurrence never waits for
+// global memory inside a chunk.
 template <int ROWS, int CHUNK>
 __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(ScanParams p) {
     pdl_prologue();
     constexpr int DKP = SCAN_LANES * ROWS;                    // padded key width
-    constexpr int PER_TOKEN = 3 * DKP + SCAN_COLS + 1;        // q | k | g | v of this CTA's columns | beta
+    constexpr int PER_TOKEN = 3 * DKP + SCAN_COLS + 4;        // q | k | g | v of this CTA's columns | beta and three unused
     constexpr int STAGED = CHUNK * PER_TOKEN;
-    constexpr int FETCH = (STAGED + SCAN_THREADS - 1) / SCAN_THREADS;
-    __shared__ float stage_s[2][STAGED];
+    __shared__ __align__(16) float stage_s[2][STAGED];
     const int col_blocks = (p.DV + SCAN_COLS - 1) / SCAN_COLS;
     const int cb = blockIdx.x % col_blocks, h = (blockIdx.x / col_blocks) % p.H, a = blockIdx.x / (col_blocks * p.H);
     const int part = threadIdx.x & (SCAN_LANES - 1);
@@ -139,75 +153,111 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(ScanParams p) 
         return;
     }
     const int kvh = h / (p.H / p.G);
-    const int row0 = part * ROWS;
+    auto row_of = [&](int i) { return (i >> 2) * 32 + part * 4 + (i & 3); };
     float S[ROWS];
     float* st = p.state + (((size_t)slot * p.H + h) * p.DK) * p.DV;
     const bool fresh = p.seq_pos0[a] == 0;
 #pragma unroll
     for (int i = 0; i < ROWS; ++i)
-        S[i] = (!fresh && col_ok && row0 + i < p.DK) ? st[(size_t)(row0 + i) * p.DV + col] : 0.0f;
+        S[i] = (!fresh && col_ok && row_of(i) < p.DK) ? st[(size_t)row_of(i) * p.DV + col] : 0.0f;
 
-    // element e of a chunk's staging area, for the chunk that begins at token `first`
-    auto fetch = [&](int first, int e) -> float {
-        const int tok = e / PER_TOKEN, w = e % PER_TOKEN;
-        if (e >= STAGED || first + tok >= n) return 0.0f;
-        const size_t t = (size_t)start + first + tok;
-        if (w < 3 * DKP) {
+    const float* const q_base = p.qn + ((size_t)start * p.G + kvh) * p.DK;
+    const float* const k_base = p.kn + ((size_t)start * p.G + kvh) * p.DK;
+    const float* const g_base = p.g + ((size_t)start * p.H + h) * p.DK;
+    const float* const v_base = p.v + (size_t)start * p.ld_v + (size_t)h * p.DV;
+    const float* const b_base = p.beta + (size_t)start * p.H + h;
+    const size_t qk_pitch = (size_t)p.G * p.DK, g_pitch = (size_t)p.H * p.DK;
+    // the chunk that begins at token `first` into staging buffer `buf`; padding (rows beyond DK, columns beyond DV,
+    // tokens beyond the sequence's) becomes zero: a zero k and q keep such rows of S at zero whatever g is
+    auto stage = [&](int first, int buf) {
+        if (p.vec) {                             // every row a multiple of four floats and 16-byte aligned: four at a time
+            constexpr int UNITS = 3 * DKP / 4 + SCAN_COLS / 4 + 1;
+            for (int e = threadIdx.x; e < CHUNK * UNITS; e += SCAN_THREADS) {
+                const int tok = e / UNITS, u = e % UNITS;
+                const bool live = first + tok < n;
+                const size_t t = live ? (size_t)(first + tok) : 0;
+                float* to = &stage_s[buf][tok * PER_TOKEN];
+                if (u < 3 * DKP / 4) {
+                    const int which = u / (DKP / 4), c = (u % (DKP / 4)) * 4;
+                    const bool real = c < p.DK;
+                    const float* at = (which == 0 ? q_base + t * qk_pitch : (which == 1 ? k_base + t * qk_pitch : g_base + t * g_pitch)) + (real ? c : 0);
+                    copy_async_f32x4(to + which * DKP + c, at, live && real);
+                } else if (u < UNITS - 1) {
+                    const int c = (u - 3 * DKP / 4) * 4, vc = cb * SCAN_COLS + c;
+                    const bool real = vc < p.DV;
+                    copy_async_f32x4(to + 3 * DKP + c, v_base + t * p.ld_v + (real ? vc : 0), live && real);
+                } else {
+                    copy_async_f32(to + 3 * DKP + SCAN_COLS, b_base + t * p.H, live);
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            return;
+        }
+        for (int e = threadIdx.x; e < STAGED; e += SCAN_THREADS) {
+            const int tok = e / PER_TOKEN, w = e % PER_TOKEN;
+            const bool live = first + tok < n;
+            const size_t t = live ? (size_t)(first + tok) : 0;
             const int which = w / DKP, c = w % DKP;
-            if (c >= p.DK) return which == 2 ? 1.0f : 0.0f;
-            return which == 0 ? p.qn[(t * p.G + kvh) * p.DK + c] : (which == 1 ? p.kn[(t * p.G + kvh) * p.DK + c] : p.g[(t * p.H + h) * p.DK + c]);
+            const int vc = cb * SCAN_COLS + (w - 3 * DKP);
+            const float* at;
+            bool real;
+            if (which == 0) { real = c < p.DK; at = q_base + t * qk_pitch + (real ? c : 0); }
+            else if (which == 1) { real = c < p.DK; at = k_base + t * qk_pitch + (real ? c : 0); }
+            else if (which == 2) { real = c < p.DK; at = g_base + t * g_pitch + (real ? c : 0); }
+            else if (w < 3 * DKP + SCAN_COLS) { real = vc < p.DV; at = v_base + t * p.ld_v + (real ? vc : 0); }
+            else { real = w == 3 * DKP + SCAN_COLS; at = b_base + t * p.H; }
+            copy_async_f32(&stage_s[buf][e], at, live && real);
         }
-        if (w < 3 * DKP + SCAN_COLS) {
-            const int c = cb * SCAN_COLS + (w - 3 * DKP);
-            return c < p.DV ? p.v[t * p.ld_v + (size_t)h * p.DV + c] : 0.0f;
-        }
-        return p.beta[t * p.H + h];
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    float next[FETCH];
-#pragma unroll
-    for (int f = 0; f < FETCH; ++f) {
-        const int e = threadIdx.x + f * SCAN_THREADS;
-        if (e < STAGED) stage_s[0][e] = fetch(0, e);
-    }
+    stage(0, 0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     for (int first = 0, buf = 0; first < n; first += CHUNK, buf ^= 1) {
-        const bool more = first + CHUNK < n;
-        if (more) {
-#pragma unroll
-            for (int f = 0; f < FETCH; ++f) next[f] = fetch(first + CHUNK, threadIdx.x + f * SCAN_THREADS);
-        }
+        if (first + CHUNK < n) stage(first + CHUNK, buf ^ 1);
         const int count = min(CHUNK, n - first);
         for (int tok = 0; tok < count; ++tok) {
             const float* row = stage_s[buf] + tok * PER_TOKEN;
-            const float* qs = row + row0; const float* ks = row + DKP + row0; const float* gs = row + 2 * DKP + row0;
+            const float4* qs = reinterpret_cast<const float4*>(row) + part;
+            const float4* ks = reinterpret_cast<const float4*>(row + DKP) + part;
+            const float4* gs = reinterpret_cast<const float4*>(row + 2 * DKP) + part;
             const float v = row[3 * DKP + local_col], beta = row[3 * DKP + SCAN_COLS];
-            float dot = 0.0f;
+            float4 kk[ROWS / 4];
+            float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;          // four chains instead of one (always the same four)
 #pragma unroll
-            for (int i = 0; i < ROWS; ++i) { S[i] *= gs[i]; dot = fmaf(S[i], ks[i], dot); }
+            for (int j = 0; j < ROWS / 4; ++j) {
+                const float4 gg = gs[j * 8];
+                kk[j] = ks[j * 8];
+                S[4 * j + 0] *= gg.x; S[4 * j + 1] *= gg.y; S[4 * j + 2] *= gg.z; S[4 * j + 3] *= gg.w;
+                d0 = fmaf(S[4 * j + 0], kk[j].x, d0); d1 = fmaf(S[4 * j + 1], kk[j].y, d1);
+                d2 = fmaf(S[4 * j + 2], kk[j].z, d2); d3 = fmaf(S[4 * j + 3], kk[j].w, d3);
+            }
+            float dot = (d0 + d1) + (d2 + d3);
             dot += __shfl_xor_sync(0xffffffffu, dot, 1);
             dot += __shfl_xor_sync(0xffffffffu, dot, 2);
             dot += __shfl_xor_sync(0xffffffffu, dot, 4);
             const float u = beta * (v - dot);
-            float out = 0.0f;
+            float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < ROWS; ++i) { S[i] = fmaf(ks[i], u, S[i]); out = fmaf(S[i], qs[i], out); }
+            for (int j = 0; j < ROWS / 4; ++j) {
+                const float4 qq = qs[j * 8];
+                S[4 * j + 0] = fmaf(kk[j].x, u, S[4 * j + 0]); S[4 * j + 1] = fmaf(kk[j].y, u, S[4 * j + 1]);
+                S[4 * j + 2] = fmaf(kk[j].z, u, S[4 * j + 2]); S[4 * j + 3] = fmaf(kk[j].w, u, S[4 * j + 3]);
+                o0 = fmaf(S[4 * j + 0], qq.x, o0); o1 = fmaf(S[4 * j + 1], qq.y, o1);
+                o2 = fmaf(S[4 * j + 2], qq.z, o2); o3 = fmaf(S[4 * j + 3], qq.w, o3);
+            }
+            float out = (o0 + o1) + (o2 + o3);
             out += __shfl_xor_sync(0xffffffffu, out, 1);
             out += __shfl_xor_sync(0xffffffffu, out, 2);
             out += __shfl_xor_sync(0xffffffffu, out, 4);
             if (part == 0 && col_ok) p.o[((size_t)start + first + tok) * ((size_t)p.H * p.DV) + (size_t)h * p.DV + col] = out;
         }
-        if (more) {
-#pragma unroll
-            for (int f = 0; f < FETCH; ++f) {
-                const int e = threadIdx.x + f * SCAN_THREADS;
-                if (e < STAGED) stage_s[buf ^ 1][e] = next[f];
-            }
-        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
     }
 #pragma unroll
     for (int i = 0; i < ROWS; ++i)
-        if (col_ok && row0 + i < p.DK) st[(size_t)(row0 + i) * p.DV + col] = S[i];
+        if (col_ok && row_of(i) < p.DK) st[(size_t)row_of(i) * p.DV + col] = S[i];
 }
 
 // ------------------------------------------------------------------------------ output norm and gate
@@ -301,7 +351,9 @@ MLB_EXPORT int mlb_delta_scan(const float* qn, const float* kn, const float* g, 
     if (!qn || !kn || !g || !beta || !v || !o || !state || !slots || !seq_starts || !seq_pos0)
         return fail(MLB_INVALID_ARGUMENT, "delta_scan: null operand");
     if (A == 0) return MLB_OK;
-    ScanParams p{qn, kn, g, beta, v, ld_v, o, state, slots, num_slots, seq_starts, seq_pos0, A, H, G, DK, DV, error_flag};
+    const bool aligned = ((uintptr_t)qn | (uintptr_t)kn | (uintptr_t)g | (uintptr_t)v) % 16 == 0;
+    const int vec = aligned && DK % 4 == 0 && DV % 4 == 0 && ld_v % 4 == 0;
+    ScanParams p{qn, kn, g, beta, v, ld_v, o, state, slots, num_slots, seq_starts, seq_pos0, A, H, G, DK, DV, vec, error_flag};
     const unsigned blocks = (unsigned)((long long)A * H * ((DV + SCAN_COLS - 1) / SCAN_COLS));
     if (DK <= 32) launch_kernel(delta_scan_kernel<4, 16>, blocks, SCAN_THREADS, 0, stream, p);
     else if (DK <= 64) launch_kernel(delta_scan_kernel<8, 16>, blocks, SCAN_THREADS, 0, stream, p);

@@ -29,15 +29,45 @@ struct LnParams {
     int width; float eps;
 };
 
+// sum over the partial results at one float4, eight loads in flight, added in split order
+__device__ __forceinline__ float4 partial_sum4(const float* at, int n, long long stride) {
+    float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k0 = 0; k0 < n; k0 += 8) {
+        float4 part[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            part[k] = k0 + k < n ? *reinterpret_cast<const float4*>(at + (size_t)(k0 + k) * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { total.x += part[k].x; total.y += part[k].y; total.z += part[k].z; total.w += part[k].w; }
+    }
+    return total;
+}
+
 template <typename OutT, bool ADD>
 __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(LnParams p) {
     pdl_prologue();
-    extern __shared__ float row_s[];
+    extern __shared__ __align__(16) float row_s[];
     __shared__ float scratch[32];
     const int r = blockIdx.x, W = p.width;
     const size_t src = (!ADD && p.rows) ? (size_t)p.rows[r] : (size_t)r;
     float* xr = p.x + src * W;
     float sum = 0.0f;
+    if (ADD && (W & 3) == 0) {
+        // four columns a thread, the partial results' loads issued eight at a time (they are independent; only their sum
+        // is taken in split order)
+        for (int c = threadIdx.x * 4; c < W; c += LN_THREADS * 4) {
+            float4 v = *reinterpret_cast<const float4*>(xr + c);
+            v.x *= p.alpha; v.y *= p.alpha; v.z *= p.alpha; v.w *= p.alpha;
+            const float4 a = partial_sum4(p.d1 + src * W + c, p.n1, p.stride1);
+            v.x = fmaf(p.s1, a.x, v.x); v.y = fmaf(p.s1, a.y, v.y); v.z = fmaf(p.s1, a.z, v.z); v.w = fmaf(p.s1, a.w, v.w);
+            if (p.d2) {
+                const float4 b = partial_sum4(p.d2 + src * W + c, p.n2, p.stride2);
+                v.x = fmaf(p.s2, b.x, v.x); v.y = fmaf(p.s2, b.y, v.y); v.z = fmaf(p.s2, b.z, v.z); v.w = fmaf(p.s2, b.w, v.w);
+            }
+            *reinterpret_cast<float4*>(row_s + c) = v;
+            sum += (v.x + v.y) + (v.z + v.w);
+        }
+    } else
     for (int c = threadIdx.x; c < W; c += LN_THREADS) {
         float v = xr[c];
         if (ADD) {
