@@ -63,6 +63,45 @@ __global__ void short_conv_kernel(ConvParams p) {
     p.y[(size_t)t * p.ldy + c] = acc;
 }
 
+// four channels a thread: every row a multiple of four floats and 16-byte aligned
+__global__ void short_conv_x4_kernel(ConvParams p) {
+    pdl_prologue();
+    const int C4 = p.C / 4;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)p.T * C4) return;
+    const int t = (int)(i / C4), c = (int)(i % C4) * 4;
+    const int a = p.token_seq[t];
+    const int start = p.seq_starts[a], pos0 = p.seq_pos0[a];
+    const int local = t - start;
+    const int slot = p.slots[a];
+    const bool slot_ok = slot >= 0 && slot < p.num_slots;
+    if (!slot_ok && p.error_flag) atomicExch(p.error_flag, 3);
+    const int hist = p.taps - 1;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* w = p.w + (size_t)c * p.taps;
+    for (int j = 0; j < p.taps; ++j) {
+        const int src = local - hist + j;
+        float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (src >= 0) {
+            const float* at = p.u + ((long long)start + src) * p.ld + p.col0 + c;
+            u = *reinterpret_cast<const float4*>(at);
+            for (int k = 1; k < p.n_partials; ++k) {
+                const float4 more = *reinterpret_cast<const float4*>(at + (size_t)k * p.partial_stride);
+                u.x += more.x; u.y += more.y; u.z += more.z; u.w += more.w;
+            }
+        } else if (pos0 + src >= 0 && slot_ok) {
+            u = *reinterpret_cast<const float4*>(p.state + ((size_t)slot * hist + (hist + src)) * p.C + c);
+        }
+        acc.x = fmaf(w[j], u.x, acc.x); acc.y = fmaf(w[p.taps + j], u.y, acc.y);
+        acc.z = fmaf(w[2 * p.taps + j], u.z, acc.z); acc.w = fmaf(w[3 * p.taps + j], u.w, acc.w);
+    }
+    if (p.act == 1) {
+        acc.x = acc.x / (1.0f + expf(-acc.x)); acc.y = acc.y / (1.0f + expf(-acc.y));
+        acc.z = acc.z / (1.0f + expf(-acc.z)); acc.w = acc.w / (1.0f + expf(-acc.w));
+    }
+    *reinterpret_cast<float4*>(p.y + (size_t)t * p.ldy + c) = acc;
+}
+
 __global__ void short_conv_state_kernel(ConvParams p) {
     pdl_prologue();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -107,7 +146,10 @@ MLB_EXPORT int mlb_short_conv(const float* u, long long ld, int n_partials, long
     if (!y) return fail(MLB_INVALID_ARGUMENT, "short_conv: null output");
     if (T == 0) return MLB_OK;
     const long long n = (long long)T * C;
-    launch_kernel(short_conv_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, p);
+    const bool x4 = C % 4 == 0 && ld % 4 == 0 && ldy % 4 == 0 && col0 % 4 == 0 && partial_stride % 4 == 0 &&
+                    ((uintptr_t)u | (uintptr_t)y | (uintptr_t)state) % 16 == 0;
+    if (x4) launch_kernel(short_conv_x4_kernel, (unsigned)((n / 4 + 255) / 256), 256, 0, stream, p);
+    else launch_kernel(short_conv_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, p);
     return check_launch("short_conv");
 }
 

@@ -234,8 +234,7 @@ class Model:
                 residual, delta = block.forward(residual, delta, ctx, view)
                 if sink is not None:
                     sink(f"run{i}.layer{run.layer}.residual", residual)
-                    if delta is not None:            # a block that normalises after its sums hands none on
-                        sink(f"run{i}.layer{run.layer}.delta", delta)
+                    sink(f"run{i}.layer{run.layer}.delta", delta)          # None where a block hands no delta on
                 continue
             pointers = self._run_pointers(block, view)
             if key not in recordings:
