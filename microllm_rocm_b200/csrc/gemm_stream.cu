@@ -67,6 +67,7 @@ struct StreamParams {
     int stages;
     int mode;
     int up_offset;             // SILU: first up row of the fused weight
+    int act;                   // SILU: the gate's activation (0 silu, 1 gelu_tanh)
     int tmem_cols;
 };
 
@@ -137,6 +138,12 @@ __device__ __forceinline__ float silu(float g) {
     // exponential and reciprocal: the epilogue of a one-tile CTA is not hidden behind anything, and the
     // result is rounded to bf16 right away.
     return __fdividef(g, 1.0f + __expf(-g));
+}
+// the gate's activation of a gated feed-forward: 0 = silu, 1 = the tanh form of gelu, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float gate_activation(float g, int act) {
+    if (act == 0) return silu(g);
+    const float y = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (2.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * y)));
 }
 
 // Where the 128 rows of work item `tile` come from: two boxes of 64 weight rows.
@@ -338,10 +345,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     float res[8];
                     if (!up_side) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) res[j] = silu(__uint_as_float(raw[j])) * xb[j * HALF_W + i];
+                        for (int j = 0; j < 8; ++j) res[j] = gate_activation(__uint_as_float(raw[j]), p.act) * xb[j * HALF_W + i];
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) res[j] = silu(xb[(8 + j) * HALF_W + i]) * __uint_as_float(raw[8 + j]);
+                        for (int j = 0; j < 8; ++j) res[j] = gate_activation(xb[(8 + j) * HALF_W + i], p.act) * __uint_as_float(raw[8 + j]);
                     }
                     __nv_bfloat16* dst = p.out + (size_t)(c + (up_side ? 8 : 0)) * p.ldo + f;
                     const int left = p.M - c - (up_side ? 8 : 0);
@@ -514,9 +521,21 @@ MLB_EXPORT int mlb_gemm_stream(const void* x, long long ldx, const void* w, long
 }
 
 // out[M, I] (bf16) = silu(x Wg^T) * (x Wu^T) with Wg = W rows [0, I) and Wu = W rows [up_offset, up_offset + I).
+MLB_EXPORT int mlb_gemm_stream_gated(const void* x, long long ldx, const void* w, long long ldw, int w_rows, int up_offset,
+                                     void* out, long long ldo, int M, int I, int K, int stages, int act, int* error_flag,
+                                     cudaStream_t stream);
+
 MLB_EXPORT int mlb_gemm_stream_silu(const void* x, long long ldx, const void* w, long long ldw, int w_rows, int up_offset,
                                     void* out, long long ldo, int M, int I, int K, int stages, int* error_flag,
                                     cudaStream_t stream) {
+    return mlb_gemm_stream_gated(x, ldx, w, ldw, w_rows, up_offset, out, ldo, M, I, K, stages, 0, error_flag, stream);
+}
+
+// the same with the gate's activation chosen: act = 0 silu, 1 the tanh form of gelu
+MLB_EXPORT int mlb_gemm_stream_gated(const void* x, long long ldx, const void* w, long long ldw, int w_rows, int up_offset,
+                                     void* out, long long ldo, int M, int I, int K, int stages, int act, int* error_flag,
+                                     cudaStream_t stream) {
+    if (act != 0 && act != 1) return fail(MLB_INVALID_ARGUMENT, "gemm_stream_gated: unknown activation %d", act);
     int status = check_operands(x, ldx, w, ldw, M, K);
     if (status != MLB_OK) return status;
     if (I <= 0 || up_offset < I || up_offset + I > w_rows || ldo < I || !out)
@@ -524,7 +543,7 @@ MLB_EXPORT int mlb_gemm_stream_silu(const void* x, long long ldx, const void* w,
                     I, up_offset, up_offset + I, w_rows);
     StreamParams p{};
     p.out = (__nv_bfloat16*)out; p.ldo = ldo; p.error_flag = error_flag; p.M = M; p.N = I; p.K = K;
-    p.mode = MODE_SILU; p.splits = 1; p.up_offset = up_offset;
+    p.mode = MODE_SILU; p.splits = 1; p.up_offset = up_offset; p.act = act;
     p.n_tiles = (I + HALF_W - 1) / HALF_W;
     return launch(p, x, ldx, w, ldw, w_rows, stages, stream);
 }

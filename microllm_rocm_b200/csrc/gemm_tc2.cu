@@ -57,7 +57,7 @@ struct PairParams {
     int k_blocks, stages;
     int out_bf16;
     int accumulate;            // out += result (fp32 out only)
-    int dual;                  // 1: silu(gate) * up; W rows n (gate) and up_offset + n (up); N counts gate rows
+    int dual;                  // 1: silu(gate) * up, 2: gelu_tanh(gate) * up; W rows n (gate) and up_offset + n (up); N counts gate rows
     int up_offset;
     int n_tiles, m_tiles;
 };
@@ -149,6 +149,13 @@ __device__ __forceinline__ float silu(float g) {
     // exponential overflows to +inf and the quotient is -0, which is the limit; no branch, so that the
     // 32 elements a thread holds can be evaluated side by side
     return __fdividef(g, 1.0f + __expf(-g));
+}
+// the gate's activation of a gated feed-forward: 0 = silu, 1 = the tanh form of gelu, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+// (tanh y = 1 - 2 / (1 + e^(2y)), with the fast exponential and reciprocal: the result is rounded to bf16 right away)
+__device__ __forceinline__ float gate_activation(float g, int act) {
+    if (act == 0) return silu(g);
+    const float y = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (2.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * y)));
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -283,7 +290,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                     const int tok = tok0 + c + j;
                     if (tok >= p.M) break;
                     float r = __uint_as_float(raw[j]);
-                    if (p.dual) r = silu(r) * __uint_as_float(raw_u[j]);
+                    if (p.dual) r = gate_activation(r, p.dual - 1) * __uint_as_float(raw_u[j]);
                     r += bias;
                     if (p.out_bf16) ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldo + f] = __float2bfloat16_rn(r);
                     else {
@@ -339,13 +346,15 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 }  // namespace
 
 // y[M, N] = x[M, K] * W[N, K]^T (+ bias) (+ y when accumulate), or, with dual,
-// y[M, N] = silu(x Wg^T) * (x Wu^T) where Wg = W rows [0, N) and Wu = W rows [up_offset, up_offset + N).
+// y[M, N] = act(x Wg^T) * (x Wu^T) where Wg = W rows [0, N) and Wu = W rows [up_offset, up_offset + N); dual = 1: act = silu,
+// dual = 2: the tanh form of gelu.
 // x and W are bf16 with row pitches ldx, ldw (elements); K and the pitches must be multiples of 8 and the
 // bases 16-byte aligned (TMA).  sm_count: SMs to use (an even number; CTAs come in pairs).
 MLB_EXPORT int mlb_gemm_pair(const void* x, long long ldx, const void* w, long long ldw, int w_rows, const float* bias,
                              void* out, long long ldo, int out_bf16, int accumulate, int dual, int up_offset, int M, int N,
                              int K, int stages, int sm_count, int* error_flag, cudaStream_t stream) {
     if (M < 0 || N <= 0 || K <= 0) return fail(MLB_INVALID_ARGUMENT, "gemm_pair: bad sizes M=%d N=%d K=%d", M, N, K);
+    if (dual < 0 || dual > 2) return fail(MLB_INVALID_ARGUMENT, "gemm_pair: dual must be 0, 1 (silu) or 2 (gelu_tanh)");
     if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ldx < K || ldw < K)
         return fail(MLB_UNSUPPORTED_SIZE, "gemm_pair: K=%d and the row pitches (%lld, %lld) must be multiples of 8 elements", K, ldx, ldw);
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return fail(MLB_UNSUPPORTED_SIZE, "gemm_pair: operands must be 16-byte aligned");

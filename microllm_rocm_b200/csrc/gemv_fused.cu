@@ -108,6 +108,7 @@ struct SiluParams {
     __nv_bfloat16* out;          // [M, ldo]
     long long ldx, ldw, ldo;
     int M, I, K, up_offset, x_stride;
+    int act;                     // the gate's activation: 0 silu, 1 gelu_tanh
 };
 
 constexpr int SILU_WARPS = 4;
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(SILU_WARPS * 32) gemv_silu_kernel(SiluParams p
             gate += red[((w * 2 + 0) * NT * 4 + ne) * 32 + l2];
             up += red[((w * 2 + 1) * NT * 4 + ne) * 32 + l2];
         }
-        if (row < p.I && tok < p.M) p.out[(size_t)tok * p.ldo + row] = __float2bfloat16_rn(silu(gate) * up);
+        if (row < p.I && tok < p.M) p.out[(size_t)tok * p.ldo + row] = __float2bfloat16_rn(gate_activation(gate, p.act) * up);
     }
 }
 
@@ -347,15 +348,25 @@ int check_operands(const char* what, const void* x, long long ldx, const void* w
 MLB_EXPORT int mlb_gemv_fused_max_k() { return 6144; }
 
 // out[M, I] (bf16) = silu(x Wg^T) * (x Wu^T), Wg = W rows [0, I), Wu = W rows [up_offset, up_offset + I)
+MLB_EXPORT int mlb_gemv_gated(const void* x, long long ldx, const void* w, long long ldw, int w_rows, int up_offset, void* out,
+                              long long ldo, int M, int I, int K, int act, cudaStream_t stream);
+
 MLB_EXPORT int mlb_gemv_silu(const void* x, long long ldx, const void* w, long long ldw, int w_rows, int up_offset, void* out,
                              long long ldo, int M, int I, int K, cudaStream_t stream) {
+    return mlb_gemv_gated(x, ldx, w, ldw, w_rows, up_offset, out, ldo, M, I, K, 0, stream);
+}
+
+// the same with the gate's activation chosen: act = 0 silu, 1 the tanh form of gelu
+MLB_EXPORT int mlb_gemv_gated(const void* x, long long ldx, const void* w, long long ldw, int w_rows, int up_offset, void* out,
+                              long long ldo, int M, int I, int K, int act, cudaStream_t stream) {
+    if (act != 0 && act != 1) return fail(MLB_INVALID_ARGUMENT, "gemv_gated: unknown activation %d", act);
     int status = check_operands("gemv_silu", x, ldx, w, ldw, M, K);
     if (status != MLB_OK) return status;
     if (I <= 0 || up_offset < I || up_offset + I > w_rows || ldo < I || !out)
         return fail(MLB_INVALID_ARGUMENT, "gemv_silu: gate rows [0, %d) and up rows [%d, %d) must lie inside the weight's %d rows", I, up_offset, up_offset + I, w_rows);
     if (K > mlb_gemv_fused_max_k()) return fail(MLB_UNSUPPORTED_SIZE, "gemv_silu: K=%d is more than %d", K, mlb_gemv_fused_max_k());
     const int nt = M <= 8 ? 1 : 2;
-    SiluParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldx, ldw, ldo, M, I, K, up_offset, x_pitch(K)};
+    SiluParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldx, ldw, ldo, M, I, K, up_offset, x_pitch(K), act};
     const size_t smem = (size_t)nt * 8 * p.x_stride * 2 + (size_t)SILU_WARPS * 2 * nt * 4 * 32 * sizeof(float);
     static size_t configured1_on[MAX_DEVICES] = {0}, configured2_on[MAX_DEVICES] = {0};   // per device, as the attribute is
     size_t& configured1 = configured1_on[device_index()];

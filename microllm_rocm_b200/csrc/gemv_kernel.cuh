@@ -35,6 +35,12 @@ __device__ __forceinline__ float silu(float g) {
     return g * e / (1.0f + e);
 }
 
+// the gate's activation of a gated feed-forward: 0 = silu, 1 = the tanh form of gelu, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float gate_activation(float g, int act) {
+    if (act == 0) return silu(g);
+    return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+
 struct GemvParams {
     const __nv_bfloat16* x;      // [M, ldx]
     const __nv_bfloat16* w;      // [rows, ldw]

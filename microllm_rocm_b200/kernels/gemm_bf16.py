@@ -29,6 +29,7 @@ ops.register_signatures("gemv_fused.cu", {
                        c_int, c_void_p],
     "mlb_gemv_silu": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_int, c_int,
                       c_void_p],
+    "mlb_gemv_gated": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p],
     "mlb_gemv_qkv_rope": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                           c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                           c_void_p],
@@ -49,6 +50,7 @@ ops.register_signatures("gemm_stream.cu", {
                         c_int, c_void_p, c_void_p],
     "mlb_gemm_stream_silu": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_int,
                              c_int, c_int, c_void_p, c_void_p],
+    "mlb_gemm_stream_gated": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
 })
 
 _error_flags = {}
@@ -177,15 +179,16 @@ def gemv_split_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[to
     return partial
 
 
-def gemv_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, I] (bf16) = silu(x @ weight[:I]^T) * (x @ weight[I:2I]^T), one kernel, no partial sums."""
+def gemv_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[M, I] (bf16) = act(x @ weight[:I]^T) * (x @ weight[I:2I]^T), one kernel, no partial sums; act = "silu" or
+    "gelu_tanh" (`ops.ACTIVATIONS`)."""
     M, K = x.shape
     I = out.shape[1]
     if weight.shape != (2 * I, K) or out.shape[0] != M or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         raise KernelError("gemv_silu_mul: the weight must hold gate rows then up rows, the output be bf16 [M, I]")
     L = ops.lib("gemv_fused.cu")
-    build.check(L, L.mlb_gemv_silu(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), 2 * I, I, out.data_ptr(),
-                                   out.stride(0), M, I, K, ops._stream()))
+    build.check(L, L.mlb_gemv_gated(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), 2 * I, I, out.data_ptr(),
+                                    out.stride(0), M, I, K, ops.ACTIVATIONS[activation], ops._stream()))
 
 
 def gemv_qkv_rope(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
@@ -279,16 +282,18 @@ def stream_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
 
 
 def stream_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, stages: int = 0,
-                    error_flag: Optional[torch.Tensor] = None) -> None:
-    """out[M, I] (bf16) = silu(x @ weight[:I]^T) * (x @ weight[I:2I]^T), the activation as the product's epilogue."""
+                    error_flag: Optional[torch.Tensor] = None, activation: str = "silu") -> None:
+    """out[M, I] (bf16) = act(x @ weight[:I]^T) * (x @ weight[I:2I]^T), the activation ("silu" or "gelu_tanh") as the
+    product's epilogue."""
     M, K = x.shape
     I = out.shape[1]
     if weight.shape != (2 * I, K) or out.shape[0] != M or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         raise KernelError("stream_silu_mul: the weight must hold gate rows then up rows, the output be bf16 [M, I]")
     flag = error_flag if error_flag is not None else device_error_flag(x.device)
     L = ops.lib("gemm_stream.cu")
-    build.check(L, L.mlb_gemm_stream_silu(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), 2 * I, I,
-                                          out.data_ptr(), out.stride(0), M, I, K, int(stages), flag.data_ptr(), ops._stream()))
+    build.check(L, L.mlb_gemm_stream_gated(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), 2 * I, I,
+                                           out.data_ptr(), out.stride(0), M, I, K, int(stages), ops.ACTIVATIONS[activation],
+                                           flag.data_ptr(), ops._stream()))
 
 
 # ------------------------------------------------------------------------------ prompt portions: CTA pairs
@@ -312,10 +317,10 @@ def supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
               accumulate: bool = False, dual_rows: Optional[int] = None, stages: int = 0, sms: Optional[int] = None,
-              error_flag: Optional[torch.Tensor] = None) -> None:
+              error_flag: Optional[torch.Tensor] = None, activation: str = "silu") -> None:
     """The CTA-pair tcgen05 product (`gemm_tc2.cu`) for prompt-sized token counts:
     out[M, N] = x[M, K] @ weight[:N]^T (+ bias) (+ out), or with dual_rows = I:
-    out[M, I] = silu(x @ weight[:I]^T) * (x @ weight[I:2I]^T)."""
+    out[M, I] = act(x @ weight[:I]^T) * (x @ weight[I:2I]^T), act = "silu" or "gelu_tanh"."""
     M, K = x.shape
     dual = dual_rows is not None
     N = dual_rows if dual else weight.shape[0]
@@ -331,7 +336,7 @@ def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Op
     L = ops.lib("gemm_tc2.cu")
     build.check(L, L.mlb_gemm_pair(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), weight.shape[0],
                                    ops._ptr(bias), out.data_ptr(), out.stride(0), 1 if out.dtype == torch.bfloat16 else 0,
-                                   1 if accumulate else 0, 1 if dual else 0, N if dual else 0, M, N, K, int(stages),
+                                   1 if accumulate else 0, 1 + ops.ACTIVATIONS[activation] if dual else 0, N if dual else 0, M, N, K, int(stages),
                                    int(sms), flag.data_ptr(), ops._stream()))
 
 

@@ -127,6 +127,34 @@ def test_gated_activation_with_the_tanh_form_of_gelu(dtype):
     assert torch.allclose(out.double(), plain.gelu_tanh(s[:, :8]) * s[:, 8:], atol=1e-5)
 
 
+@pytest.mark.parametrize("tokens", [3, 8, 20, 64, 130, 300])
+def test_gated_feed_forward_with_gelu_on_every_product_kernel(tokens):
+    """The feed-forward part alone in bf16 at token counts that take each of its routes (the few-token kernels with the
+    activation as their epilogue or behind partial sums, the streaming kernel, the library product with the activation
+    kernel, the CTA-pair kernel) against float64 on the same bf16 weights; silu on the same routes must differ."""
+    from microllm_rocm_b200.engine.loading import prepare_kernels
+    from microllm_rocm_b200.parts.base import FEED_FORWARDS, Runtime
+    torch.manual_seed(tokens)
+    hidden, inter = 256, 768
+    rt = Runtime(torch.device(DEV), torch.bfloat16)
+    names = ("gate", "up", "down")
+    w = {"gate": torch.randn(inter, hidden, device=DEV) * hidden ** -0.5, "up": torch.randn(inter, hidden, device=DEV) * hidden ** -0.5,
+         "down": torch.randn(hidden, inter, device=DEV) * inter ** -0.5}
+    w = {k: v.to(torch.bfloat16) for k, v in w.items()}
+    x = (torch.randn(tokens, hidden, device=DEV) * 1.5).to(torch.bfloat16)
+    outs = {}
+    for activation in ("gelu_tanh", "silu"):
+        part = FEED_FORWARDS["swiglu"](dict(hidden_size=hidden, intermediate_size=inter, names=names, activation=activation), rt)
+        prepare_kernels(SimpleNamespace(parts=lambda: [part]))
+        part.bind(dict(w))
+        y = part.forward(x, None)
+        outs[activation] = (y.sum(0) if y.dim() == 3 else y).double().cpu()
+    xd, wd = x.double().cpu(), {k: v.double().cpu() for k, v in w.items()}
+    want = (plain.gelu_tanh(xd @ wd["gate"].T) * (xd @ wd["up"].T)) @ wd["down"].T
+    assert float((outs["gelu_tanh"] - want).abs().max() / want.abs().max()) < 0.02
+    assert float((outs["silu"] - want).abs().max() / want.abs().max()) > 0.05
+
+
 @pytest.mark.parametrize("C, col0", [(10, 3), (12, 4)])           # one channel a thread; four (rows of whole 16-byte pieces)
 @pytest.mark.parametrize("taps", [2, 4, 7])
 def test_short_convolution_over_steps_with_slots_used_again(taps, C, col0):
