@@ -355,10 +355,18 @@ MLB_EXPORT int mlb_delta_scan(const float* qn, const float* kn, const float* g, 
     const int vec = aligned && DK % 4 == 0 && DV % 4 == 0 && ld_v % 4 == 0;
     ScanParams p{qn, kn, g, beta, v, ld_v, o, state, slots, num_slots, seq_starts, seq_pos0, A, H, G, DK, DV, vec, error_flag};
     const unsigned blocks = (unsigned)((long long)A * H * ((DV + SCAN_COLS - 1) / SCAN_COLS));
-    if (DK <= 32) launch_kernel(delta_scan_kernel<4, 16>, blocks, SCAN_THREADS, 0, stream, p);
-    else if (DK <= 64) launch_kernel(delta_scan_kernel<8, 16>, blocks, SCAN_THREADS, 0, stream, p);
-    else if (DK <= 128) launch_kernel(delta_scan_kernel<16, 8>, blocks, SCAN_THREADS, 0, stream, p);
-    else launch_kernel(delta_scan_kernel<32, 4>, blocks, SCAN_THREADS, 0, stream, p);
+    // A handful of long-running CTAs (a prompt portion: one CTA walks all its tokens) must be spread one to an SM.  Started
+    // early behind a predecessor that still fills the SMs, they land wherever a slot falls free, several on one SM, and
+    // the slowest SM decides: such a launch waits for its predecessor the plain way.  Many short CTAs (decoding) start early.
+    const bool early = blocks > 2u * (unsigned)sm_count();
+    auto go = [&](auto kernel) {
+        if (early) launch_kernel(kernel, blocks, SCAN_THREADS, 0, stream, p);
+        else kernel<<<blocks, SCAN_THREADS, 0, stream>>>(p);
+    };
+    if (DK <= 32) go(delta_scan_kernel<4, 16>);
+    else if (DK <= 64) go(delta_scan_kernel<8, 16>);
+    else if (DK <= 128) go(delta_scan_kernel<16, 8>);
+    else go(delta_scan_kernel<32, 4>);
     return check_launch("delta_scan");
 }
 

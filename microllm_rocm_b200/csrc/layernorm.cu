@@ -43,12 +43,71 @@ __device__ __forceinline__ float4 partial_sum4(const float* at, int n, long long
     return total;
 }
 
-template <typename OutT, bool ADD>
+constexpr int LN_VECS = 4;          // float4 a thread keeps in registers: rows of up to 4 * LN_VECS * LN_THREADS columns
+
+// FEW: a step of few rows (decoding), where what counts is the time from the predecessor's end to this kernel's:
+// weight and bias wait in registers.  Many rows: fewer registers a thread, more rows in flight on an SM.
+template <typename OutT, bool ADD, bool FEW>
 __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(LnParams p) {
-    pdl_prologue();
+    pdl_launch_dependents();
     extern __shared__ __align__(16) float row_s[];
     __shared__ float scratch[32];
     const int r = blockIdx.x, W = p.width;
+    if (ADD && (W & 3) == 0 && W <= 4 * LN_VECS * LN_THREADS) {
+        // The row stays in registers between the passes.  Weight and bias are never written by a kernel: they are
+        // fetched before the wait for the predecessor.
+        float4 wv[FEW ? LN_VECS : 1], bv[FEW ? LN_VECS : 1], v[LN_VECS];
+        if (FEW) {
+#pragma unroll
+            for (int i = 0; i < LN_VECS; ++i) {
+                const int c = (threadIdx.x + i * LN_THREADS) * 4;
+                if (c < W) { wv[i] = *reinterpret_cast<const float4*>(p.weight + c); bv[i] = *reinterpret_cast<const float4*>(p.bias + c); }
+            }
+        }
+        pdl_wait();
+        float* xr = p.x + (size_t)r * W;
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < LN_VECS; ++i) {
+            const int c = (threadIdx.x + i * LN_THREADS) * 4;
+            if (c >= W) break;
+            float4 x = *reinterpret_cast<const float4*>(xr + c);
+            x.x *= p.alpha; x.y *= p.alpha; x.z *= p.alpha; x.w *= p.alpha;
+            const float4 a = partial_sum4(p.d1 + (size_t)r * W + c, p.n1, p.stride1);
+            x.x = fmaf(p.s1, a.x, x.x); x.y = fmaf(p.s1, a.y, x.y); x.z = fmaf(p.s1, a.z, x.z); x.w = fmaf(p.s1, a.w, x.w);
+            if (p.d2) {
+                const float4 b = partial_sum4(p.d2 + (size_t)r * W + c, p.n2, p.stride2);
+                x.x = fmaf(p.s2, b.x, x.x); x.y = fmaf(p.s2, b.y, x.y); x.z = fmaf(p.s2, b.z, x.z); x.w = fmaf(p.s2, b.w, x.w);
+            }
+            v[i] = x;
+            sum += (x.x + x.y) + (x.z + x.w);
+        }
+        const float mean = block_sum(sum, scratch) / (float)W;
+        float sq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < LN_VECS; ++i) {
+            const int c = (threadIdx.x + i * LN_THREADS) * 4;
+            if (c >= W) break;
+            v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+            sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+        }
+        const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)W + p.eps);
+        OutT* yr = p.out ? (OutT*)p.out + (size_t)r * W : nullptr;
+#pragma unroll
+        for (int i = 0; i < LN_VECS; ++i) {
+            const int c = (threadIdx.x + i * LN_THREADS) * 4;
+            if (c >= W) break;
+            const float4 w4 = FEW ? wv[FEW ? i : 0] : *reinterpret_cast<const float4*>(p.weight + c);
+            const float4 b4 = FEW ? bv[FEW ? i : 0] : *reinterpret_cast<const float4*>(p.bias + c);
+            float4 y;
+            y.x = v[i].x * inv * w4.x + b4.x; y.y = v[i].y * inv * w4.y + b4.y;
+            y.z = v[i].z * inv * w4.z + b4.z; y.w = v[i].w * inv * w4.w + b4.w;
+            *reinterpret_cast<float4*>(xr + c) = y;
+            if (yr) { yr[c] = from_f32<OutT>(y.x); yr[c + 1] = from_f32<OutT>(y.y); yr[c + 2] = from_f32<OutT>(y.z); yr[c + 3] = from_f32<OutT>(y.w); }
+        }
+        return;
+    }
+    pdl_wait();
     const size_t src = (!ADD && p.rows) ? (size_t)p.rows[r] : (size_t)r;
     float* xr = p.x + src * W;
     float sum = 0.0f;
@@ -101,10 +160,11 @@ int launch(const LnParams& p, int n, int out_dtype, bool add, cudaStream_t strea
     if ((size_t)p.width * sizeof(float) > 200 * 1024) return fail(MLB_UNSUPPORTED_SIZE, "%s: a row of %d floats does not fit shared memory", what, p.width);
     if (n == 0) return MLB_OK;
     const size_t smem = (size_t)p.width * sizeof(float);
+    const bool few = add && n <= 2 * sm_count();
     auto go = [&](auto kernel) -> int {
         if (smem > 48 * 1024) {
-            static bool raised[MAX_DEVICES][4] = {};
-            const int slot = (add ? 2 : 0) + (out_dtype == MLB_BF16 ? 1 : 0);
+            static bool raised[MAX_DEVICES][8] = {};
+            const int slot = (few ? 4 : 0) + (add ? 2 : 0) + (out_dtype == MLB_BF16 ? 1 : 0);
             if (!raised[device_index()][slot]) {
                 if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
                     return fail(MLB_CUDA_ERROR, "%s: cannot raise the shared-memory limit", what);
@@ -114,8 +174,9 @@ int launch(const LnParams& p, int n, int out_dtype, bool add, cudaStream_t strea
         launch_kernel(kernel, (unsigned)n, LN_THREADS, smem, stream, p);
         return check_launch(what);
     };
-    if (add) return out_dtype == MLB_BF16 ? go(layernorm_kernel<__nv_bfloat16, true>) : go(layernorm_kernel<float, true>);
-    return out_dtype == MLB_BF16 ? go(layernorm_kernel<__nv_bfloat16, false>) : go(layernorm_kernel<float, false>);
+    if (add && few) return out_dtype == MLB_BF16 ? go(layernorm_kernel<__nv_bfloat16, true, true>) : go(layernorm_kernel<float, true, true>);
+    if (add) return out_dtype == MLB_BF16 ? go(layernorm_kernel<__nv_bfloat16, true, false>) : go(layernorm_kernel<float, true, false>);
+    return out_dtype == MLB_BF16 ? go(layernorm_kernel<__nv_bfloat16, false, false>) : go(layernorm_kernel<float, false, false>);
 }
 
 }  // namespace
