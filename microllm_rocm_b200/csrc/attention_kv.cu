@@ -59,14 +59,23 @@ __global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p)
     if (item >= (long long)p.T * items) return;
     const int t = (int)(item / items), which = (int)(item % items);
     const int pos = p.positions[t];
-    // where the item goes
-    KVT* page_row = nullptr;
     const bool is_q = which < p.H, is_k = !is_q && which < p.H + p.G;
     const int head = is_q ? which : (is_k ? which - p.H : which - p.H - p.G);
     const int D = (is_q || is_k) ? p.DK : p.DV;
     const int P = (is_q || is_k) ? p.PK : p.PV;       // stored width
+    if (!is_q && !p.pages) return;
+    // the row's elements first: their loads need nothing of the page lookup below and travel while it runs
+    const Columns& src = is_q ? p.q : (is_k ? p.k : p.v);
+    const int col = (is_q ? p.q_col : (is_k ? p.k_col : p.v_col)) + head * D;
+    float x[PER_LANE];
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int c = lane + 32 * i;
+        x[i] = c < D ? src.at(t, col + c) : 0.0f;
+    }
+    // where the item goes
+    KVT* page_row = nullptr;
     if (!is_q) {
-        if (!p.pages) return;
         const int seq = p.token_seq[t];
         const int block = pos / p.page_size;
         const int page = block < p.max_blocks ? p.block_table[(size_t)seq * p.max_blocks + block] : -1;
@@ -79,16 +88,9 @@ __global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p)
                                    : (size_t)p.G * p.page_size * p.PK + ((size_t)head * p.page_size + pos % p.page_size) * p.PV;
         page_row = (KVT*)p.pages + (size_t)page * page_stride + within;
     }
-    const Columns& src = is_q ? p.q : (is_k ? p.k : p.v);
-    const int col = (is_q ? p.q_col : (is_k ? p.k_col : p.v_col)) + head * D;
-    float x[PER_LANE];
     float ss = 0.0f;
 #pragma unroll
-    for (int i = 0; i < PER_LANE; ++i) {
-        const int c = lane + 32 * i;
-        x[i] = c < D ? src.at(t, col + c) : 0.0f;
-        ss = fmaf(x[i], x[i], ss);
-    }
+    for (int i = 0; i < PER_LANE; ++i) ss = fmaf(x[i], x[i], ss);
     if (is_q || is_k) {
         const float* w = is_q ? p.q_norm : p.k_norm;
         if (w) {
