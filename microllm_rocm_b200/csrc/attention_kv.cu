@@ -50,7 +50,8 @@ struct PrepareParams {
     int* error_flag;
 };
 
-template <typename OutT, typename KVT>
+// NL: elements a lane holds (the widest stored row is at most 32 * NL elements)
+template <typename OutT, typename KVT, int NL>
 __global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p) {
     pdl_prologue();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -67,9 +68,9 @@ __global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p)
     // the row's elements first: their loads need nothing of the page lookup below and travel while it runs
     const Columns& src = is_q ? p.q : (is_k ? p.k : p.v);
     const int col = (is_q ? p.q_col : (is_k ? p.k_col : p.v_col)) + head * D;
-    float x[PER_LANE];
+    float x[NL];
 #pragma unroll
-    for (int i = 0; i < PER_LANE; ++i) {
+    for (int i = 0; i < NL; ++i) {
         const int c = lane + 32 * i;
         x[i] = c < D ? src.at(t, col + c) : 0.0f;
     }
@@ -90,20 +91,20 @@ __global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p)
     }
     float ss = 0.0f;
 #pragma unroll
-    for (int i = 0; i < PER_LANE; ++i) ss = fmaf(x[i], x[i], ss);
+    for (int i = 0; i < NL; ++i) ss = fmaf(x[i], x[i], ss);
     if (is_q || is_k) {
         const float* w = is_q ? p.q_norm : p.k_norm;
         if (w) {
             const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)D + p.eps);
 #pragma unroll
-            for (int i = 0; i < PER_LANE; ++i) {
+            for (int i = 0; i < NL; ++i) {
                 const int c = lane + 32 * i;
                 if (c < D) x[i] = x[i] * inv * w[c];
             }
         }
         if (p.freq && p.rot_dims > 0) {
 #pragma unroll
-            for (int i = 0; i < PER_LANE; ++i) {
+            for (int i = 0; i < NL; ++i) {
                 const int c = lane + 32 * i;
                 const float other = __shfl_xor_sync(0xffffffffu, x[i], 1);     // the pair's other element sits in the next lane
                 if (c < p.rot_dims) {
@@ -116,16 +117,16 @@ __global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p)
         if (is_q && p.temp_every > 0) {
             const float temp = 1.0f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.0f);
 #pragma unroll
-            for (int i = 0; i < PER_LANE; ++i) x[i] *= temp;
+            for (int i = 0; i < NL; ++i) x[i] *= temp;
         }
     }
     if (is_q) {
         OutT* out = (OutT*)p.q_out + ((size_t)t * p.H + head) * P;
 #pragma unroll
-        for (int i = 0; i < PER_LANE; ++i) { const int c = lane + 32 * i; if (c < P) out[c] = from_f32<OutT>(c < D ? x[i] : 0.0f); }
+        for (int i = 0; i < NL; ++i) { const int c = lane + 32 * i; if (c < P) out[c] = from_f32<OutT>(c < D ? x[i] : 0.0f); }
     } else {
 #pragma unroll
-        for (int i = 0; i < PER_LANE; ++i) { const int c = lane + 32 * i; if (c < P) page_row[c] = from_f32<KVT>(c < D ? x[i] : 0.0f); }
+        for (int i = 0; i < NL; ++i) { const int c = lane + 32 * i; if (c < P) page_row[c] = from_f32<KVT>(c < D ? x[i] : 0.0f); }
     }
 }
 
@@ -293,9 +294,20 @@ MLB_EXPORT int mlb_qk_prepare(const float* src, long long ld, int n_partials, lo
     const long long items = (long long)T * (H + 2 * G);
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
     const int kvd = pages ? kv_dtype : q_dtype;
-    if (q_dtype == MLB_F32 && kvd == MLB_F32) launch_kernel(qk_prepare_kernel<float, float>, blocks, WARPS * 32, 0, stream, p);
-    else if (q_dtype == MLB_BF16 && kvd == MLB_BF16) launch_kernel(qk_prepare_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, WARPS * 32, 0, stream, p);
-    else if (q_dtype == MLB_F32 && kvd == MLB_BF16) launch_kernel(qk_prepare_kernel<float, __nv_bfloat16>, blocks, WARPS * 32, 0, stream, p);
+    const int widest = stored_k > stored_v ? stored_k : stored_v;
+    auto go = [&](auto k1, auto k2, auto k4, auto k8) {
+        if (widest <= 32) launch_kernel(k1, blocks, WARPS * 32, 0, stream, p);
+        else if (widest <= 64) launch_kernel(k2, blocks, WARPS * 32, 0, stream, p);
+        else if (widest <= 128) launch_kernel(k4, blocks, WARPS * 32, 0, stream, p);
+        else launch_kernel(k8, blocks, WARPS * 32, 0, stream, p);
+    };
+    typedef __nv_bfloat16 bf;
+    if (q_dtype == MLB_F32 && kvd == MLB_F32)
+        go(qk_prepare_kernel<float, float, 1>, qk_prepare_kernel<float, float, 2>, qk_prepare_kernel<float, float, 4>, qk_prepare_kernel<float, float, 8>);
+    else if (q_dtype == MLB_BF16 && kvd == MLB_BF16)
+        go(qk_prepare_kernel<bf, bf, 1>, qk_prepare_kernel<bf, bf, 2>, qk_prepare_kernel<bf, bf, 4>, qk_prepare_kernel<bf, bf, 8>);
+    else if (q_dtype == MLB_F32 && kvd == MLB_BF16)
+        go(qk_prepare_kernel<float, bf, 1>, qk_prepare_kernel<float, bf, 2>, qk_prepare_kernel<float, bf, 4>, qk_prepare_kernel<float, bf, 8>);
     else return fail(MLB_INVALID_ARGUMENT, "qk_prepare: unsupported dtypes %d/%d", q_dtype, kv_dtype);
     return check_launch("qk_prepare");
 }
