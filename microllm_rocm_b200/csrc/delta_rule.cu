@@ -8,7 +8,7 @@
 //   mlb_delta_scan      the recurrence over the new tokens of every sequence of the step, from the state in the
 //                       sequence's slot ([slots, H, DK, DV] fp32; taken as zero when the sequence starts at position 0)
 //                       and back into it.  The columns of S never meet: a CTA owns 16 of them for one (sequence,
-//                       head), eight lanes share a column's DK rows in registers and meet by shuffles twice a token.
+//                       head), eight or sixteen lanes share a column's DK rows in registers and meet by shuffles twice a token.
 //   mlb_delta_output    o / rms(o) per head * weight * sigmoid(W2g a_g), stored in the compute dtype.
 //
 // The order of every addition depends on the token's place in its sequence only, never on how the sequence was cut
@@ -114,7 +114,7 @@ struct ScanParams {
     int* error_flag;
 };
 
-constexpr int SCAN_LANES = 8, SCAN_THREADS = 128, SCAN_COLS = SCAN_THREADS / SCAN_LANES;
+constexpr int SCAN_COLS = 16;            // columns of S a CTA owns; its threads: SCAN_COLS * LANES
 
 __device__ __forceinline__ void copy_async_f32(float* to_shared, const float* from, bool real) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(to_shared);
@@ -128,14 +128,17 @@ __device__ __forceinline__ void copy_async_f32x4(float* to_shared, const float* 
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(from), "r"(bytes) : "memory");
 }
 
-// ROWS: rows of a column that one lane keeps (DK <= 8 * ROWS, ROWS a multiple of 4): lane `part` of a column owns rows
-// 32 j + 4 part + (0..3), so that the eight lanes of a column read 128 consecutive bytes of q, k and g at a time.
+// LANES lanes share a column; ROWS: rows of the column that one lane keeps (DK <= LANES * ROWS, ROWS a multiple of 4): lane
+// `part` owns rows 4 LANES j + 4 part + (0..3), so that the lanes of a column read consecutive 16-byte pieces of q, k and g.
+// Sixteen lanes a column give an SM eight warps instead of four for the same columns: a token's chain of dependent
+// instructions is what the kernel waits for, and two warps a scheduler fill each other's gaps.
 // CHUNK: tokens whose q, k, g, v and beta are staged in shared memory at a time; the next chunk is copied there
 // asynchronously (cp.async, zero fill for padding) while the present one is computed, so the recurrence never waits for
 // global memory inside a chunk.
-template <int ROWS, int CHUNK>
-__global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(ScanParams p) {
+template <int LANES, int ROWS, int CHUNK>
+__global__ void __launch_bounds__(SCAN_COLS * LANES) delta_scan_kernel(ScanParams p) {
     pdl_prologue();
+    constexpr int SCAN_LANES = LANES, SCAN_THREADS = SCAN_COLS * LANES;
     constexpr int DKP = SCAN_LANES * ROWS;                    // padded key width
     constexpr int PER_TOKEN = 3 * DKP + SCAN_COLS + 4;        // q | k | g | v of this CTA's columns | beta and three unused
     constexpr int STAGED = CHUNK * PER_TOKEN;
@@ -153,7 +156,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(ScanParams p) 
         return;
     }
     const int kvh = h / (p.H / p.G);
-    auto row_of = [&](int i) { return (i >> 2) * 32 + part * 4 + (i & 3); };
+    auto row_of = [&](int i) { return (i >> 2) * (4 * LANES) + part * 4 + (i & 3); };
     float S[ROWS];
     float* st = p.state + (((size_t)slot * p.H + h) * p.DK) * p.DV;
     const bool fresh = p.seq_pos0[a] == 0;
@@ -216,7 +219,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(ScanParams p) 
     for (int first = 0, buf = 0; first < n; first += CHUNK, buf ^= 1) {
         if (first + CHUNK < n) stage(first + CHUNK, buf ^ 1);
         const int count = min(CHUNK, n - first);
-        for (int tok = 0; tok < count; ++tok) {
+        float* const o_at = p.o + ((size_t)start + first) * ((size_t)p.H * p.DV) + (size_t)h * p.DV + col;
+        auto token = [&](int tok) {
             const float* row = stage_s[buf] + tok * PER_TOKEN;
             const float4* qs = reinterpret_cast<const float4*>(row) + part;
             const float4* ks = reinterpret_cast<const float4*>(row + DKP) + part;
@@ -226,8 +230,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(ScanParams p) 
             float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;          // four chains instead of one (always the same four)
 #pragma unroll
             for (int j = 0; j < ROWS / 4; ++j) {
-                const float4 gg = gs[j * 8];
-                kk[j] = ks[j * 8];
+                const float4 gg = gs[j * LANES];
+                kk[j] = ks[j * LANES];
                 S[4 * j + 0] *= gg.x; S[4 * j + 1] *= gg.y; S[4 * j + 2] *= gg.z; S[4 * j + 3] *= gg.w;
                 d0 = fmaf(S[4 * j + 0], kk[j].x, d0); d1 = fmaf(S[4 * j + 1], kk[j].y, d1);
                 d2 = fmaf(S[4 * j + 2], kk[j].z, d2); d3 = fmaf(S[4 * j + 3], kk[j].w, d3);
@@ -236,11 +240,12 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(ScanParams p) 
             dot += __shfl_xor_sync(0xffffffffu, dot, 1);
             dot += __shfl_xor_sync(0xffffffffu, dot, 2);
             dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+            if (LANES == 16) dot += __shfl_xor_sync(0xffffffffu, dot, 8);
             const float u = beta * (v - dot);
             float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
             for (int j = 0; j < ROWS / 4; ++j) {
-                const float4 qq = qs[j * 8];
+                const float4 qq = qs[j * LANES];
                 S[4 * j + 0] = fmaf(kk[j].x, u, S[4 * j + 0]); S[4 * j + 1] = fmaf(kk[j].y, u, S[4 * j + 1]);
                 S[4 * j + 2] = fmaf(kk[j].z, u, S[4 * j + 2]); S[4 * j + 3] = fmaf(kk[j].w, u, S[4 * j + 3]);
                 o0 = fmaf(S[4 * j + 0], qq.x, o0); o1 = fmaf(S[4 * j + 1], qq.y, o1);
@@ -250,7 +255,14 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(ScanParams p) 
             out += __shfl_xor_sync(0xffffffffu, out, 1);
             out += __shfl_xor_sync(0xffffffffu, out, 2);
             out += __shfl_xor_sync(0xffffffffu, out, 4);
-            if (part == 0 && col_ok) p.o[((size_t)start + first + tok) * ((size_t)p.H * p.DV) + (size_t)h * p.DV + col] = out;
+            if (LANES == 16) out += __shfl_xor_sync(0xffffffffu, out, 8);
+            if (part == 0 && col_ok) o_at[(size_t)tok * ((size_t)p.H * p.DV)] = out;
+        };
+        if (count == CHUNK) {            // a whole chunk: unrolled, so that a token's read-out runs beside the next token's update
+#pragma unroll
+            for (int tok = 0; tok < CHUNK; ++tok) token(tok);
+        } else {
+            for (int tok = 0; tok < count; ++tok) token(tok);
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
@@ -359,14 +371,14 @@ MLB_EXPORT int mlb_delta_scan(const float* qn, const float* kn, const float* g, 
     // early behind a predecessor that still fills the SMs, they land wherever a slot falls free, several on one SM, and
     // the slowest SM decides: such a launch waits for its predecessor the plain way.  Many short CTAs (decoding) start early.
     const bool early = blocks > 2u * (unsigned)sm_count();
-    auto go = [&](auto kernel) {
-        if (early) launch_kernel(kernel, blocks, SCAN_THREADS, 0, stream, p);
-        else kernel<<<blocks, SCAN_THREADS, 0, stream>>>(p);
+    auto go = [&](auto kernel, int lanes) {
+        if (early) launch_kernel(kernel, blocks, SCAN_COLS * lanes, 0, stream, p);
+        else kernel<<<blocks, SCAN_COLS * lanes, 0, stream>>>(p);
     };
-    if (DK <= 32) go(delta_scan_kernel<4, 16>);
-    else if (DK <= 64) go(delta_scan_kernel<8, 16>);
-    else if (DK <= 128) go(delta_scan_kernel<16, 8>);
-    else go(delta_scan_kernel<32, 4>);
+    if (DK <= 32) go(delta_scan_kernel<8, 4, 16>, 8);
+    else if (DK <= 64) go(delta_scan_kernel<16, 4, 16>, 16);
+    else if (DK <= 128) go(delta_scan_kernel<16, 8, 8>, 16);
+    else go(delta_scan_kernel<16, 16, 4>, 16);
     return check_launch("delta_scan");
 }
 

@@ -49,10 +49,10 @@ CASES = {
                      attention(1, 1, 18, 0, rot_dims=4, base=777.0, scaling={"factor": 1.5, "original": 16, "fast": 4.0, "slow": 1.0})],
           "ranks": (3, 9)},
     # sizes the tensor-core kernels like (heads of 64 with equal widths in the attention layer; 32 / 64 on the left)
-    "c": {"architecture": "Matidra", "vocab": 256, "width": 128, "norm": {"eps": 1e-6}, "postln_alpha": 3.0,
-          "layers": [attention(4, 2, 64, 256, rot_dims=32, base=1e6, scaling={"factor": 2.0, "original": 128, "fast": 16.0, "slow": 1.0}),
-                     parallel((4, 2, 32, 64, 4, (0.3, 32)), (2, 2, 64, 64, 4), 256, left_scale=0.6, right_scale=1.1),
-                     parallel((4, 2, 32, 64, 4, (0.3, 32)), (2, 2, 64, 64, 4), 256, left_scale=0.6, right_scale=1.1)],
+    "c": {"architecture": "Matidra", "vocab": 256, "width": 128, "norm": {"eps": 2e-6}, "postln_alpha": 2.0,
+          "layers": [attention(4, 2, 64, 256, rot_dims=32, base=5e5, scaling={"factor": 3.0, "original": 128, "fast": 16.0, "slow": 1.0}),
+                     parallel((4, 2, 32, 64, 4, (0.25, 32)), (2, 2, 64, 64, 4), 256, left_scale=0.8, right_scale=0.9),
+                     parallel((4, 2, 32, 64, 4, (0.25, 32)), (2, 2, 64, 64, 4), 256, left_scale=0.8, right_scale=0.9)],
           "ranks": (16, 16)},
     # only parallel layers, one head each side, no rotation anywhere, wide keys on the right (several registers a lane)
     "d": {"architecture": "Matidra", "vocab": 150, "width": 48, "norm": {"eps": 1e-5}, "postln_alpha": 0.5,

@@ -98,7 +98,7 @@ def test_no_convolution_means_no_convolution_state():
 def test_stretched_frequencies_equal_the_plain_ones():
     from microllm_rocm_b200.parts.rotary import stretched_frequencies
     for dims, base, sc in ((12, 5000.0, {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 2.0}),
-                           (32, 1e6, {"factor": 2.0, "original": 128, "fast": 16.0, "slow": 1.0}),
+                           (32, 5e5, {"factor": 3.0, "original": 128, "fast": 16.0, "slow": 1.0}),
                            (4, 777.0, {"factor": 1.5, "original": 16, "fast": 4.0, "slow": 1.0})):
         freq, magnitude = stretched_frequencies(base, dims, sc)
         want, want_magnitude = plain.stretched_frequencies(dims, base, sc)

@@ -98,8 +98,8 @@ def test_layer_norm_plain_and_after_a_weighted_sum(out_dtype):
         assert torch.allclose(out.double(), want, atol=1e-5 if out_dtype == torch.float32 else 0.05)
         d1, d2 = torch.randn(3, 9, width, device=DEV), torch.randn(9, width, device=DEV)          # three partial sums; one plain term
         stream, copy = x.clone(), torch.empty(9, width, dtype=out_dtype, device=DEV)
-        ops.scale_add_layernorm(stream, 2.5, [(0.6, d1), (1.1, d2)], w, b, 1e-5, copy)
-        want = plain.layer_norm(2.5 * x.double() + 0.6 * d1.double().sum(0) + 1.1 * d2.double(), w.double(), b.double(), 1e-5)
+        ops.scale_add_layernorm(stream, 2.5, [(0.7, d1), (1.3, d2)], w, b, 1e-5, copy)
+        want = plain.layer_norm(2.5 * x.double() + 0.7 * d1.double().sum(0) + 1.3 * d2.double(), w.double(), b.double(), 1e-5)
         assert torch.allclose(stream.double(), want, atol=2e-5)
         assert torch.allclose(copy.double(), want, atol=1e-5 if out_dtype == torch.float32 else 0.05)
         one = x.clone()
