@@ -160,8 +160,8 @@ class NormedAttention(Mixer):
       short causal convolution over time on every channel of q, k, v (`conv` taps > 1; weights [channels, taps], the last
           column is the current token's; the last taps - 1 projected rows of a sequence are kept in its state slot)
       per-head rms norm of q and k with one weight each, shared by the heads (`qk_norm`)
-      rotation by the position encoding's table: any even part of the head, split-half or interleaved pairs... this
-          mixer's kernel turns interleaved pairs (2i, 2i + 1); cosines and sines times the table's magnitude
+      rotation of the first `rotary_dim` elements of every head by the position encoding's table, in interleaved
+          pairs (2i, 2i + 1), cosines and sines times the table's magnitude (a split-half table is refused)
       q times 1 + coef * ln(floor((p + 1) / every) + 1) at position p (`q_temp = (coef, every)`)
       score = q . k * scale, causal (optionally the last `window` keys), softmax
       concat_heads(o) * sigmoid(Wg x) (`gate`), then Wo
