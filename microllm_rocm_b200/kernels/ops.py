@@ -166,7 +166,7 @@ def all_sources():
     check compiles."""
     from . import attention
     out = base_sources()
-    for d in (32, 64, 128):
+    for d in (32, 64, 128, 256):
         out += attention.mma_sources(d) + attention.tc_sources(d)
     from . import gemm_bf16, latent
     return (out + gemm_bf16.sources() + [("gemv_noalloc.cu", {})] + part_sources()

@@ -24,7 +24,7 @@ from .base import Mixer, PagedKVNeed, PagedKVView, PositionEncoding, Runtime, St
 
 
 ROPE_TABLE_MIN_TOKENS = 64          # from here on a step-wide table of sines and cosines pays
-SHARED_KERNEL_WIDTHS = (32, 64, 128)   # head sizes at which the tensor-core attention kernels of one width are built and tested
+SHARED_KERNEL_WIDTHS = (32, 64, 128, 256)   # head sizes at which the tensor-core attention kernels of one width are built and tested
 
 
 @register_mixer("attention")
@@ -214,9 +214,7 @@ class NormedAttention(Mixer):
         # and always in fp32, where every kernel is a plain one)
         self.stored = None
         if not rt.is_fp32:
-            wide = -(-max(self.dk, self.dv) // 32) * 32
-            if wide in SHARED_KERNEL_WIDTHS:
-                self.stored = wide
+            self.stored = next((w for w in SHARED_KERNEL_WIDTHS if w >= max(self.dk, self.dv)), None)
         self.w_in = self.w_o = self.q_norm_w = self.k_norm_w = self.w_conv = None
 
     # --- declarations -----------------------------------------------------------------

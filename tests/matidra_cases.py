@@ -59,6 +59,12 @@ CASES = {
           "layers": [parallel((1, 1, 40, 16, 2, (1.0, 3)), (1, 1, 136, 40, 3), 64, left_scale=2.0, right_scale=0.25),
                      parallel((1, 1, 40, 16, 2, (1.0, 3)), (1, 1, 136, 40, 3), 64, left_scale=2.0, right_scale=0.25)],
           "ranks": (7, 4)},
+    # wide heads: keys of 80 beside values of 160 on the left (stored at 256 on the tensor-core kernels), 72 / 72 in the
+    # attention layer (stored at 128), all of a head turned
+    "e": {"architecture": "Matidra", "vocab": 120, "width": 96, "norm": {"eps": 1e-5}, "postln_alpha": 1.5,
+          "layers": [parallel((2, 1, 80, 160, 3, (0.5, 5)), (2, 2, 24, 48, 4), 128, left_scale=0.9, right_scale=0.8),
+                     attention(2, 1, 72, 128, rot_dims=72, base=2000.0)],
+          "ranks": (8, 8)},
 }
 
 

@@ -305,3 +305,41 @@ def test_two_layers_of_the_benchmark_shape_against_the_plain_implementation(dtyp
           f"at largest |logit| {float(size.max()):.3f}; per row relative {[round(float(e / s), 5) for e, s in zip(err, size)]}")
     limit = 3e-5 if dtype == "float32" else 0.02           # of the row's largest |logit|; measured 3.3e-6 and 0.0074
     assert bool((err <= limit * size).all()), (err / size).tolist()
+
+
+@gpu
+@pytest.mark.parametrize("d", [32, 64, 256])
+def test_other_head_sizes_at_long_contexts(d):
+    """The kernels of one width at the head sizes beside 128 (a mixer with unequal key and value widths stores both at the
+    next of 32, 64, 128, 256): a decode step of eight uneven sequences up to 4,096 keys with a planted far key (key
+    splits over a cluster), and prompt portions of 600 and 37 new tokens behind 2,400 and 900 keys."""
+    nh, nkv, page = 8, 2, 16
+    lens = [max(41, 4096 - 311 * i) for i in range(8)]
+    case = PagedCase(lens, nkv, d, page, seed=d)
+    gen = case.gen
+    q = (torch.randn((8, nh, d), generator=gen, device=DEV) * PEAK).bfloat16()
+    direction = torch.randn(d, generator=gen, device=DEV)
+    direction /= direction.norm()
+    strength = PLANT * (d / 128.0) ** 0.25                # the same margin of the planted score at every head size
+    fars = [(s * 997 + 3) % n for s, n in enumerate(lens)]
+    for s, far in enumerate(fars):
+        case.plant(s, far, direction, strength)
+    q[:, :nh // 2] = (direction * strength).bfloat16()
+    out, _, _, plans = launch(case, [q[s:s + 1] for s in range(8)], [1] * 8, nh, nkv, d, None)
+    assert plans and plans[0][3] > 1, "the decode step was meant to split its keys"
+    out = out.reshape(8, nh, d)
+    worst = 0.0
+    for s, n in enumerate(lens):
+        k, v = case.dense(s)
+        worst = max(worst, worst_relative_error(out[s:s + 1], reference_rows(q[s:s + 1].float(), torch.tensor([n - 1]), k, v, None)))
+        assert (out[s, 0] - v[fars[s], 0]).abs().max() < 0.05, s
+    lens, news = [3000, 937], [600, 37]
+    case = PagedCase(lens, nkv, d, page, seed=d + 1)
+    qs = [(torch.randn((n, nh, d), generator=case.gen, device=DEV) * PEAK).bfloat16() for n in news]
+    out, starts, pos0, _ = launch(case, qs, news, nh, nkv, d, None)
+    for s, n in enumerate(news):
+        k, v = case.dense(s)
+        want = reference_rows(qs[s].float(), torch.arange(pos0[s], pos0[s] + n), k, v, None)
+        worst = max(worst, worst_relative_error(out[starts[s]:starts[s + 1]].reshape(n, nh, d), want))
+    print(f"head size {d}: worst relative row error {worst:.4f}")
+    assert worst < BF16_ROW_TOL, worst

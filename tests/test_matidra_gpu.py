@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 FP32_TOL = 3e-5          # of the largest |logit|
 BF16_TOL = 0.05          # of the largest |logit|
 DEV = "cuda:0"
-LENGTHS = {"a": [1, 2, 37, 130], "b": [5, 64, 99], "c": [3, 50, 290], "d": [17, 80]}
+LENGTHS = {"a": [1, 2, 37, 130], "b": [5, 64, 99], "c": [3, 50, 290], "d": [17, 80], "e": [9, 200]}
 
 
 def tol(dtype):
@@ -346,7 +346,7 @@ def test_one_request_at_a_time(folders, key, dtype, cut):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["a", "c"])
+@pytest.mark.parametrize("key", ["a", "c", "e"])
 def test_mixed_batches_over_a_tight_pool(folders, key, dtype):
     """Up to four live requests, portions beside single tokens, some left out of a step; the pool holds just the peak and
     there are four state slots for ten requests, so pages and slots go from one request to the next (a slot's old state
@@ -374,18 +374,19 @@ def test_fp32_does_not_depend_on_cuts_batches_or_pages(folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_far_keys_and_page_borders_decide_the_output(tmp_path_factory, dtype):
+@pytest.mark.parametrize("key", ["c", "e"])
+def test_far_keys_and_page_borders_decide_the_output(tmp_path_factory, dtype, key):
     """Peaky softmax (the queries' norm weights scaled up): single keys, far back and at page borders, carry a
     position's output, in a prompt of several hundred tokens and in the tokens decoded after it, with two page sizes."""
-    raw, weights = case("c", seed=11, sharp=6.0)
+    raw, weights = case(key, seed=11, sharp=6.0)
     folder = write_folder(str(tmp_path_factory.mktemp("matidra_sharp")), raw, weights)
     reqs = {"long": random_tokens(700, raw["vocab"], 21), "edge": random_tokens(16 * 9 + 1, raw["vocab"], 22)}
     for page_size, steps in ((16, steps_prefill_then_decode(reqs, tail=40)), (32, steps_portions(reqs, sizes=(127, 2, 33, 1, 64, 300)))):
         got = collect(engine_for(folder, dtype, max_tokens=1100, page_size=page_size), steps)
-        compare(got, "c-sharp", raw, weights, reqs, dtype)
+        compare(got, key + "-sharp", raw, weights, reqs, dtype)
     # the softmax really is peaky: with the plain norm weights the logits are far from these
     a = plain.forward(raw, weights, reqs["edge"][:60])
-    b = plain.forward(raw, case("c", seed=11, sharp=1.0)[1], reqs["edge"][:60])
+    b = plain.forward(raw, case(key, seed=11, sharp=1.0)[1], reqs["edge"][:60])
     assert float((a - b).abs().max() / a.abs().max()) > 3 * BF16_TOL
 
 
