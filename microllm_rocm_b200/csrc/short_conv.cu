@@ -49,9 +49,9 @@ __global__ void short_conv_kernel(ConvParams p) {
     const int start = p.seq_starts[a], pos0 = p.seq_pos0[a];
     const int local = t - start;
     const int slot = p.slots[a];
-    const bool slot_ok = slot >= 0 && slot < p.num_slots;
-    if (!slot_ok && p.error_flag) atomicExch(p.error_flag, 3);
     const int hist = p.taps - 1;
+    const bool slot_ok = hist == 0 || (slot >= 0 && slot < p.num_slots);      // one tap keeps no state: any slot will do
+    if (!slot_ok && p.error_flag) atomicExch(p.error_flag, 3);
     float acc = 0.0f;
     for (int j = 0; j < p.taps; ++j) {
         const int src = local - hist + j;              // index among this step's tokens of the sequence

@@ -54,15 +54,17 @@ CASES = {
                      parallel((4, 2, 32, 64, 4, (0.25, 32)), (2, 2, 64, 64, 4), 256, left_scale=0.8, right_scale=0.9),
                      parallel((4, 2, 32, 64, 4, (0.25, 32)), (2, 2, 64, 64, 4), 256, left_scale=0.8, right_scale=0.9)],
           "ranks": (16, 16)},
-    # only parallel layers, one head each side, no rotation anywhere, wide keys on the right (several registers a lane)
+    # one head each side, no rotation anywhere (the attention layer has none either, and no feed-forward), wide keys on the
+    # right (several registers a lane)
     "d": {"architecture": "Matidra", "vocab": 150, "width": 48, "norm": {"eps": 1e-5}, "postln_alpha": 0.5,
           "layers": [parallel((1, 1, 40, 16, 2, (1.0, 3)), (1, 1, 136, 40, 3), 64, left_scale=2.0, right_scale=0.25),
-                     parallel((1, 1, 40, 16, 2, (1.0, 3)), (1, 1, 136, 40, 3), 64, left_scale=2.0, right_scale=0.25)],
+                     parallel((1, 1, 40, 16, 2, (1.0, 3)), (1, 1, 136, 40, 3), 64, left_scale=2.0, right_scale=0.25),
+                     attention(2, 2, 24, 0)],
           "ranks": (7, 4)},
     # wide heads: keys of 80 beside values of 160 on the left (stored at 256 on the tensor-core kernels), 72 / 72 in the
-    # attention layer (stored at 128), all of a head turned
+    # attention layer (stored at 128), all of a head turned; no convolution on the right; a temperature that steps at every position
     "e": {"architecture": "Matidra", "vocab": 120, "width": 96, "norm": {"eps": 1e-5}, "postln_alpha": 1.5,
-          "layers": [parallel((2, 1, 80, 160, 3, (0.5, 5)), (2, 2, 24, 48, 4), 128, left_scale=0.9, right_scale=0.8),
+          "layers": [parallel((2, 1, 80, 160, 3, (0.5, 1)), (2, 2, 24, 48, 1), 128, left_scale=0.9, right_scale=0.8),
                      attention(2, 1, 72, 128, rot_dims=72, base=2000.0)],
           "ranks": (8, 8)},
 }
